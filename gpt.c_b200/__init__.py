@@ -1,0 +1,150 @@
+"""B200-native causal self-attention for gpt.c: ctypes access to ``libattn_sm100.so``.
+
+The product is the C-ABI library declared in ``include/attn_sm100.h`` (hand-written sm_100a CUDA).
+This package only loads it and offers a thin convenience layer that takes ``torch`` CUDA tensors
+for device memory and streams; every call goes through the C ABI with raw pointers.  There is no
+CPU or PyTorch fallback: if the library is missing or the device is not an sm_100 GPU the calls
+raise.
+
+The directory name contains a dot, so it cannot be imported with a plain ``import`` statement;
+load it with ``importlib`` (see ``load_package`` in ``__graft_entry__.py``) under the module name
+``gptc_b200``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libattn_sm100.so")
+HEADER_PATH = os.path.join(HERE, "..", "include", "attn_sm100.h")
+
+FLAG_FORCE_GENERIC = 1
+
+# name -> (restype, argtypes); must list every function include/attn_sm100.h declares
+_c = ctypes
+SIGNATURES = {
+    "attn_sm100_version": (_c.c_int, []),
+    "attn_sm100_init": (_c.c_int, []),
+    "attn_sm100_saved_bytes": (_c.c_size_t, [_c.c_int] * 4),
+    "attn_sm100_backward_scratch_bytes": (_c.c_size_t, [_c.c_int] * 4),
+    "attn_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 5 + [_c.c_void_p]),
+    "attn_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 5 + [_c.c_void_p]),
+    "attn_sm100_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
+    "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
+}
+
+_lib = None
+
+
+class AttnError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        self.code = code
+        msg = lib().attn_sm100_strerror(code).decode()
+        super().__init__(f"{where} failed with status {code}: {msg}")
+
+
+def lib() -> ctypes.CDLL:
+    """Load libattn_sm100.so (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python gpt.c_b200/build.py`; there is no fallback path")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def _check(code: int, where: str) -> None:
+    if code != 0:
+        raise AttnError(code, where)
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def init() -> None:
+    _check(lib().attn_sm100_init(), "attn_sm100_init")
+
+
+def device_status(clear: bool = True) -> int:
+    """Synchronise the current device and return its kernel status word (0 = fine)."""
+    st = ctypes.c_int(0)
+    rc = lib().attn_sm100_device_status(ctypes.byref(st), 1 if clear else 0)
+    if rc not in (0, -6):
+        raise AttnError(rc, "attn_sm100_device_status")
+    return st.value
+
+
+def saved_bytes(B: int, T: int, H: int, D: int) -> int:
+    return lib().attn_sm100_saved_bytes(B, T, H, D)
+
+
+def backward_scratch_bytes(B: int, T: int, H: int, D: int) -> int:
+    return lib().attn_sm100_backward_scratch_bytes(B, T, H, D)
+
+
+class Saved:
+    """What forward leaves behind for backward (all device buffers, owned by torch)."""
+
+    def __init__(self, saved, out, lse, shape, flags):
+        self.saved, self.out, self.lse, self.shape, self.flags = saved, out, lse, shape, flags
+
+
+def forward_into(qkv, out, out_copy, lse, saved, n_heads: int, flags: int = 0, stream=None) -> None:
+    """Raw call: every buffer is supplied by the caller (torch CUDA tensors or None)."""
+    import torch
+
+    B, T, C3 = qkv.shape
+    D = C3 // 3 // n_heads
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().attn_sm100_forward(_ptr(qkv), _ptr(out), _ptr(out_copy), _ptr(lse), _ptr(saved), B, T, n_heads, D,
+                                    flags, s.cuda_stream), "attn_sm100_forward")
+
+
+def backward_into(saved, out, lse, dout, dqkv, scratch, n_heads: int, flags: int = 0, stream=None) -> None:
+    import torch
+
+    B, T, C = dout.shape
+    D = C // n_heads
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().attn_sm100_backward(_ptr(saved), _ptr(out), _ptr(lse), _ptr(dout), _ptr(dqkv), _ptr(scratch), B, T,
+                                     n_heads, D, flags, s.cuda_stream), "attn_sm100_backward")
+
+
+def forward(qkv, n_heads: int, flags: int = 0, keep_copy: bool = False):
+    """qkv [B, T, 3C] fp32 CUDA tensor -> (out [B, T, C], Saved)."""
+    import torch
+
+    if not (qkv.is_cuda and qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.dim() == 3):
+        raise ValueError("qkv must be a contiguous fp32 CUDA tensor of shape [B, T, 3C]")
+    B, T, C3 = qkv.shape
+    if C3 % (3 * n_heads) != 0:
+        raise ValueError("last dimension must be 3 * n_heads * head_size")
+    C = C3 // 3
+    D = C // n_heads
+    out = torch.empty((B, T, C), device=qkv.device, dtype=torch.float32)
+    out_copy = torch.empty_like(out) if keep_copy else None
+    lse = torch.empty((B, n_heads, T), device=qkv.device, dtype=torch.float32)
+    saved = torch.empty(saved_bytes(B, T, n_heads, D), device=qkv.device, dtype=torch.uint8)
+    forward_into(qkv, out, out_copy, lse, saved, n_heads, flags)
+    return out, Saved(saved, out_copy if keep_copy else out, lse, (B, T, n_heads, D), flags)
+
+
+def backward(ctx: Saved, dout):
+    """dout [B, T, C] -> dqkv [B, T, 3C] = [dq | dk | dv]."""
+    import torch
+
+    B, T, H, D = ctx.shape
+    if not (dout.is_cuda and dout.dtype == torch.float32 and dout.is_contiguous() and tuple(dout.shape) == (B, T, H * D)):
+        raise ValueError("dout must be a contiguous fp32 CUDA tensor of shape [B, T, C]")
+    dqkv = torch.empty((B, T, 3 * H * D), device=dout.device, dtype=torch.float32)
+    scratch = torch.empty(backward_scratch_bytes(B, T, H, D), device=dout.device, dtype=torch.uint8)
+    backward_into(ctx.saved, ctx.out, ctx.lse, dout, dqkv, scratch, H, ctx.flags)
+    return dqkv

@@ -1,0 +1,372 @@
+// Fused causal attention backward for sm_100a, head size 64.
+//
+// Replaces attention_backward_cuda_kernel of gpt.c (kernels/src/cuda/Attention.cu:235-324): the
+// dO unpermute, the four batched SGEMMs, the in-place softmax backward over [B,H,T,T] and the
+// permute-accumulate become one kernel that recomputes the probabilities from the saved
+// log-sum-exp and never writes a T x T matrix.
+//
+// One CTA owns one (batch, head) and one tile of 128 keys (K_j, V_j stay in shared memory) and
+// walks the query tiles i = j .. last.  Everything is computed transposed so that the key index
+// is the tensor-memory lane:
+//     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (SS, all operands K-major)
+//     P^T  = exp2(S^T * c - lse_i)        dS^T = P^T * (dP^T - delta_i)      (one thread per key)
+//     dV_j += P^T dO_i            dK_j += dS^T Q_i                  (A from tensor memory)
+//     dQ_i  = dS K_j                                                (A = dS^T tile in shared
+//                                                                    memory read MN-major)
+// dK_j and dV_j accumulate in tensor memory over the whole loop and are written once; dQ_i is
+// added into the (zeroed) dq third of the output with fp32 atomics, since other key tiles
+// contribute to the same rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
+//
+// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 tensor-memory
+// allocation, warps 4-7 compute (thread r <-> key r of the tile / query r for dQ).
+//
+// Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ0 [384,448)
+// dQ1 [448,512).  P^T and dS^T overwrite S^T and dP^T chunk by chunk: of each 32 columns the
+// first 16 take the packed hi parts and the last 16 the lo parts.
+#include "attn_internal.h"
+#include "tc05.cuh"
+
+namespace attn {
+namespace {
+
+using namespace tc05;
+
+constexpr int kTile = 128;
+constexpr int kD = 64;
+constexpr int kPlaneTile = kTile * kD * 2;  // 16 KiB
+constexpr int kThreads = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+
+struct __align__(1024) BwdSmem {
+    uint8_t k[2][kPlaneTile];      // K_j   [plane]
+    uint8_t v[2][kPlaneTile];      // V_j
+    uint8_t q[2][kPlaneTile];      // Q_i
+    uint8_t g[2][kPlaneTile];      // dO_i
+    uint8_t ds[2][2][kPlaneTile];  // dS^T  [plane][query half][128 keys x 64 queries]
+    float lse2[2][kTile];          // log-sum-exp of the query tile, in log2 units, double buffered
+    float delta[2][kTile];
+    uint64_t kv_full, q_full, q_empty, g_full, g_empty, st_full, pds_full, dq_full[2], row_bar;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+enum Site : int {
+    SITE_Q_EMPTY = 101, SITE_G_EMPTY, SITE_KV_FULL, SITE_Q_FULL, SITE_G_FULL, SITE_PDS_FULL, SITE_ST_FULL,
+    SITE_DQ_FULL_FREE, SITE_DQ_FULL_READ, SITE_DQ_FULL_LAST, SITE_ROW_BAR
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_do,
+                const float *__restrict__ lse, const float *__restrict__ delta, float *__restrict__ dqkv, int B, int T,
+                int H, float scale, float scale_log2, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    BwdSmem &sm = *reinterpret_cast<BwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int BH = B * H;
+    const int nt = (T + kTile - 1) / kTile;
+    const int jt = (int)(blockIdx.x / BH);  // key tile; tile 0 has the most work and goes first
+    const int bh = (int)(blockIdx.x % BH);
+    const int b = bh / H, h = bh % H;
+    const int C = H * kD, C3 = 3 * C;
+    const int niter = nt - jt;  // query tiles jt .. nt-1
+
+    WaitCtx ctx{&sm.abort_flag, status};
+
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        mbar_init(&sm.kv_full, 1);
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_empty, 1);
+        mbar_init(&sm.g_full, 1);
+        mbar_init(&sm.g_empty, 1);
+        mbar_init(&sm.st_full, 1);
+        mbar_init(&sm.pds_full, 128);
+        mbar_init(&sm.dq_full[0], 1);
+        mbar_init(&sm.dq_full[1], 1);
+        mbar_init(&sm.row_bar, 128);
+        fence_barrier_init();
+    }
+    if (warp == 2) {
+        tmem_alloc(&sm.tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_x);
+            tma_prefetch_desc(&map_do);
+            const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
+            mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
+            tma_load_4d(sm.k[0], &map_x, &sm.kv_full, xk, jt * kTile, b, 0);
+            tma_load_4d(sm.k[1], &map_x, &sm.kv_full, xk, jt * kTile, b, 1);
+            tma_load_4d(sm.v[0], &map_x, &sm.kv_full, xv, jt * kTile, b, 0);
+            tma_load_4d(sm.v[1], &map_x, &sm.kv_full, xv, jt * kTile, b, 1);
+            for (int n = 0; n < niter; n++) {
+                const int y = (jt + n) * kTile;
+                if (n >= 1 && !mbar_wait(&sm.q_empty, (n - 1) & 1, ctx, SITE_Q_EMPTY)) break;
+                mbar_expect_tx(&sm.q_full, 2 * kPlaneTile);
+                tma_load_4d(sm.q[0], &map_x, &sm.q_full, xq, y, b, 0);
+                tma_load_4d(sm.q[1], &map_x, &sm.q_full, xq, y, b, 1);
+                if (n >= 1 && !mbar_wait(&sm.g_empty, (n - 1) & 1, ctx, SITE_G_EMPTY)) break;
+                mbar_expect_tx(&sm.g_full, 2 * kPlaneTile);
+                tma_load_4d(sm.g[0], &map_do, &sm.g_full, h * kD, y, b, 0);
+                tma_load_4d(sm.g[1], &map_do, &sm.g_full, h * kD, y, b, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_st = idesc_bf16_f32(kTile, kTile, 0, 0);  // S^T, dP^T
+            constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);     // dV, dK (A in TMEM)
+            constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);     // dQ (A, B MN-major)
+            // K-major views (rows of 64 head-dim values)
+            const uint64_t k_km[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 16, 1024),
+                                      smem_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
+            const uint64_t v_km[2] = {smem_desc_sw128(smem_u32(sm.v[0]), 16, 1024),
+                                      smem_desc_sw128(smem_u32(sm.v[1]), 16, 1024)};
+            const uint64_t q_km[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 16, 1024),
+                                      smem_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t g_km[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 16, 1024),
+                                      smem_desc_sw128(smem_u32(sm.g[1]), 16, 1024)};
+            // MN-major views of the same bytes (the row index is the contraction index)
+            const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024),
+                                      smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
+            const uint64_t q_mn[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 1024, 1024),
+                                      smem_desc_sw128(smem_u32(sm.q[1]), 1024, 1024)};
+            const uint64_t g_mn[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 1024, 1024),
+                                      smem_desc_sw128(smem_u32(sm.g[1]), 1024, 1024)};
+            const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
+                                       smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
+
+            bool ok = mbar_wait(&sm.kv_full, 0, ctx, SITE_KV_FULL);
+            for (int n = 0; ok && n < niter; n++) {
+                const uint32_t par = n & 1;
+                if (!mbar_wait(&sm.q_full, par, ctx, SITE_Q_FULL)) break;
+                if (!mbar_wait(&sm.g_full, par, ctx, SITE_G_FULL)) break;
+                tc_fence_after_sync();
+                uint32_t acc = 0;
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kD / 16; kk++) {
+                        mma_ss(tmem + kColST, desc_advance(k_km[a], kk * 32), desc_advance(q_km[bb], kk * 32), idesc_st,
+                               acc);
+                        acc = 1;
+                    }
+                }
+                acc = 0;
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kD / 16; kk++) {
+                        mma_ss(tmem + kColDPT, desc_advance(v_km[a], kk * 32), desc_advance(g_km[bb], kk * 32),
+                               idesc_st, acc);
+                        acc = 1;
+                    }
+                }
+                tc_commit(&sm.st_full);
+
+                if (!mbar_wait(&sm.pds_full, par, ctx, SITE_PDS_FULL)) break;
+                tc_fence_after_sync();
+                // dV += P^T dO_i
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; kk++) {
+                        const uint32_t a_t = tmem + kColST + 32 * (kk >> 1) + 16 * a + 8 * (kk & 1);
+                        mma_ts(tmem + kColDV, a_t, desc_advance(g_mn[bb], kk * 2048), idesc_kv,
+                               (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&sm.g_empty);
+                // dK += dS^T Q_i
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; kk++) {
+                        const uint32_t a_t = tmem + kColDPT + 32 * (kk >> 1) + 16 * a + 8 * (kk & 1);
+                        mma_ts(tmem + kColDK, a_t, desc_advance(q_mn[bb], kk * 2048), idesc_kv,
+                               (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&sm.q_empty);
+                // dQ_i = dS K_j
+                const uint32_t d_q = tmem + kColDQ + (n & 1) * kD;
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; kk++) {
+                        mma_ss(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048), idesc_dq,
+                               (term > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&sm.dq_full[n & 1]);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ compute group ------------------------------
+        const int row = ((warp & 3) << 5) | lane;  // key inside the tile == TMEM lane; query row for dQ
+        const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
+        const uint32_t t_st = tmem + lane_addr + kColST;
+        const uint32_t t_dpt = tmem + lane_addr + kColDPT;
+        bool ok = true;
+
+        // dQ of iteration n: wait for it, scale, add into the dq third of dqkv.
+        auto flush_dq = [&](int n, int site) -> bool {
+            if (!mbar_wait_warp(&sm.dq_full[n & 1], (n >> 1) & 1, ctx, site)) return false;
+            tc_fence_after_sync();
+            const int t = (jt + n) * kTile + row;
+            float *dst = dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_addr + kColDQ + (n & 1) * kD + 32 * c, r);
+                tmem_wait_ld();
+                if (t < T) {
+#pragma unroll
+                    for (int e = 0; e < 32; e++) atomicAdd(dst + 32 * c + e, __uint_as_float(r[e]) * scale);
+                }
+            }
+            return true;
+        };
+
+        for (int n = 0; n < niter; n++) {
+            const int it = jt + n;
+            const bool diag = (n == 0);
+            const int lb = n & 1;
+            {
+                const int t = it * kTile + row;
+                sm.lse2[lb][row] = t < T ? lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
+                sm.delta[lb][row] = t < T ? delta[(size_t)bh * T + t] : 0.f;
+            }
+            // every compute thread has published its row before anyone reads the tile's statistics
+            mbar_arrive(&sm.row_bar);
+            if (!mbar_wait_warp(&sm.row_bar, n & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
+
+            if (!mbar_wait_warp(&sm.st_full, n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+            // the dS^T tile in shared memory is free once the previous dQ MMA has finished
+            if (n >= 1 && !mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t s[32], dp[32];
+                tmem_ld32(t_st + 32 * c, s);
+                tmem_ld32(t_dpt + 32 * c, dp);
+                tmem_wait_ld();
+                uint32_t ph[16], pl[16], dh[16], dl[16];
+#pragma unroll
+                for (int e = 0; e < 16; e++) {
+                    const int q0 = 32 * c + 2 * e, q1 = q0 + 1;
+                    float p0 = ex2(fmaf(__uint_as_float(s[2 * e]), scale_log2, -sm.lse2[lb][q0]));
+                    float p1 = ex2(fmaf(__uint_as_float(s[2 * e + 1]), scale_log2, -sm.lse2[lb][q1]));
+                    if (diag) {  // causal: a query sees a key only when query >= key
+                        if (q0 < row) p0 = 0.f;
+                        if (q1 < row) p1 = 0.f;
+                    }
+                    const float d0 = p0 * (__uint_as_float(dp[2 * e]) - sm.delta[lb][q0]);
+                    const float d1 = p1 * (__uint_as_float(dp[2 * e + 1]) - sm.delta[lb][q1]);
+                    split_bf16x2(p0, p1, ph[e], pl[e]);
+                    split_bf16x2(d0, d1, dh[e], dl[e]);
+                }
+                tmem_st16(t_st + 32 * c, ph);
+                tmem_st16(t_st + 32 * c + 16, pl);
+                tmem_st16(t_dpt + 32 * c, dh);
+                tmem_st16(t_dpt + 32 * c + 16, dl);
+                // dS^T row `row`, queries 32c .. 32c+31, into the 128-byte-swizzled MN-major tile:
+                // query half m = c / 2, 16-byte chunk index (4 * (c % 2) + g) ^ (row % 8).
+                uint8_t *base_h = sm.ds[0][c >> 1] + row * 128;
+                uint8_t *base_l = sm.ds[1][c >> 1] + row * 128;
+#pragma unroll
+                for (int g4 = 0; g4 < 4; g4++) {
+                    const int chunk = ((4 * (c & 1) + g4) ^ (row & 7)) * 16;
+                    *reinterpret_cast<uint4 *>(base_h + chunk) =
+                        make_uint4(dh[4 * g4], dh[4 * g4 + 1], dh[4 * g4 + 2], dh[4 * g4 + 3]);
+                    *reinterpret_cast<uint4 *>(base_l + chunk) =
+                        make_uint4(dl[4 * g4], dl[4 * g4 + 1], dl[4 * g4 + 2], dl[4 * g4 + 3]);
+                }
+            }
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.pds_full);
+
+            if (n >= 1 && !flush_dq(n - 1, SITE_DQ_FULL_READ)) { ok = false; break; }
+        }
+
+        if (ok && flush_dq(niter - 1, SITE_DQ_FULL_LAST)) {
+            // the last dQ commit also covers every dV / dK MMA
+            const int t = jt * kTile + row;
+            float *dk_dst = dqkv + ((size_t)b * T + t) * C3 + C + (size_t)h * kD;
+            float *dv_dst = dk_dst + C;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t rk[32], rv[32];
+                tmem_ld32(tmem + lane_addr + kColDK + 32 * c, rk);
+                tmem_ld32(tmem + lane_addr + kColDV + 32 * c, rv);
+                tmem_wait_ld();
+                if (t < T) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        *reinterpret_cast<float4 *>(dk_dst + 32 * c + e) =
+                            make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
+                                        __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
+                        *reinterpret_cast<float4 *>(dv_dst + 32 * c + e) =
+                            make_float4(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1]), __uint_as_float(rv[e + 2]),
+                                        __uint_as_float(rv[e + 3]));
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------ tear-down ------------------------------
+    if (sm.abort_flag) __nanosleep(50000);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace
+
+static size_t bwd_smem_bytes() { return sizeof(BwdSmem) + 1024; }
+
+cudaError_t fast_bwd_set_attributes() {
+    return cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem_bytes());
+}
+
+cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const float *lse,
+                                 const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s) {
+    const int nt = (T + kTile - 1) / kTile;
+    const unsigned grid = (unsigned)(nt * B * H);
+    const float scale = 0.125f;  // 1/sqrt(64)
+    attn_bwd_kernel<<<grid, kThreads, bwd_smem_bytes(), s>>>(map_x, map_do, lse, delta, dqkv, B, T, H, scale,
+                                                             scale * 1.4426950408889634f, status);
+    return cudaGetLastError();
+}
+
+}  // namespace attn

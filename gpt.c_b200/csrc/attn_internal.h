@@ -1,0 +1,47 @@
+// Internal launch interface between the C-ABI shim (attn_api.cu) and the kernel files.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace attn {
+
+constexpr int kGenericMaxD = 256;
+constexpr int kGenericMaxT = 8192;
+constexpr int kGenericSmemLimit = 200 * 1024;
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// One bf16 plane of n elements, padded so the next plane starts 256-byte aligned.
+inline size_t plane_bytes(size_t n) { return align_up(n * sizeof(__nv_bfloat16), 256); }
+
+// fp32 -> (hi, lo) bf16 planes, hi = bf16(x), lo = bf16(x - hi).
+cudaError_t launch_split(const float *x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, size_t n, cudaStream_t s);
+
+// rowsum(dout * out) per (b, h, t) -> delta [B, H, T]; also splits dout into bf16 planes when
+// dhi/dlo are given, and zero-fills the dq third of `dq_zero` ([B, T, 3C]) when it is given.
+cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta, __nv_bfloat16 *dhi,
+                               __nv_bfloat16 *dlo, float *dq_zero, int B, int T, int H, int D, cudaStream_t s);
+
+// General-shape SIMT kernels (any D <= kGenericMaxD, T <= kGenericMaxT).
+cudaError_t generic_set_attributes();
+cudaError_t launch_generic_forward(const float *qkv, float *out, float *out_copy, float *lse, int B, int T, int H,
+                                   int D, cudaStream_t s);
+cudaError_t launch_generic_backward(const __nv_bfloat16 *xhi, const __nv_bfloat16 *xlo, const float *lse,
+                                    const float *delta, const float *dout, float *dqkv, int B, int T, int H, int D,
+                                    cudaStream_t s);
+
+// Tensor-core (tcgen05) kernels, D == 64.  The tensor maps cover the bf16 hi/lo planes:
+//   map_x : dims {3C, T, B, 2 planes}, box {64, 128, 1, 1}, 128-byte swizzle
+//   map_do: dims { C, T, B, 2 planes}, same box
+cudaError_t fast_fwd_set_attributes();
+cudaError_t fast_bwd_set_attributes();
+cudaError_t launch_fast_forward(const CUtensorMap &map_x, float *out, float *out_copy, float *lse, int B, int T, int H,
+                                int *status, cudaStream_t s);
+cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const float *lse,
+                                 const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s);
+
+}  // namespace attn

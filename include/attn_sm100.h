@@ -1,0 +1,131 @@
+/*
+ * attn_sm100.h - C ABI of the Blackwell (sm_100a) causal self-attention library, libattn_sm100.so.
+ *
+ * The library replaces the CUDA attention path of gpt.c.  It computes, for the fused tensor
+ * qkv [B, T, 3C] (C = H*D; q | k | v thirds, head h in columns h*D .. h*D+D-1 of each third),
+ *
+ *     out[b, i, h*D:(h+1)*D] = sum_{j<=i} softmax_j( q_i . k_j / sqrt(D) ) v_j          (forward)
+ *     dqkv = [dq | dk | dv] for a given dout = dL/dout                                   (backward)
+ *
+ * in fp32 at the interface, without ever materialising the T x T score matrix.
+ *
+ * What each entry point stands in for in the reference (paths relative to the gpt.c root):
+ *
+ *   attn_sm100_init              runtime_init_cuda                 kernels/src/cuda/runtime.cu:16-29
+ *   attn_sm100_forward           attention_forward_cuda_kernel     kernels/src/cuda/Attention.cu:170-232
+ *                                (declared at kernels/src/cuda/Attention.h:9-15) together with the
+ *                                permute/mask/softmax/unpermute kernels it launches (:12-75, :114-152,
+ *                                kernels/src/cuda/Softmax.cu:7-76) and its two batched SGEMMs
+ *                                (kernels/src/cuda/Tensor.cu:178-206)
+ *   attn_sm100_backward          attention_backward_cuda_kernel    kernels/src/cuda/Attention.cu:235-324
+ *                                (declared at kernels/src/cuda/Attention.h:17-22) with
+ *                                kernels/src/cuda/Softmax.cu:78-119 and four batched SGEMMs
+ *   attn_sm100_saved_bytes,      the cache allocations of forward_attention, src/attention.c:105-120
+ *   attn_sm100_backward_scratch_bytes   and the temporaries of Attention.cu:256-258
+ *   attn_sm100_device_status     cudaCheck(cudaGetLastError()) after each launch, e.g. Attention.cu:119
+ *   attn_sm100_strerror          the CHECK_ERROR / cudaCheck message texts, include/utils.h:23,
+ *                                kernels/src/cuda/cuda_common.h:61-68
+ *
+ * The reference passes tensor_t objects (include/tensor.h:44-51) and exits the process on error.
+ * This ABI takes plain device pointers and sizes and returns a status instead, so the same entry
+ * points serve the C layer (which maps non-zero to CHECK_ERROR), a ctypes harness and a
+ * multi-GPU driver that shards the batch axis.
+ *
+ * Conventions
+ *   - All pointers are device pointers on the CURRENT CUDA device; tensors are dense, row-major,
+ *     and at least 16-byte aligned (cudaMalloc / cudaMallocAsync alignment is enough).
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *   - forward/backward only enqueue work: no allocation, no synchronisation, no host copies.
+ *   - Return value: 0 on success, a negative ATTN_ERR_* for a rejected argument, or a positive
+ *     cudaError_t when the CUDA runtime reported one.  Nothing is enqueued after an error.
+ *   - There is no CPU fallback: every path is a CUDA kernel.
+ *
+ * Precision: operands are split into two bf16 terms (x ~ hi + lo, 16 significant bits) and each
+ * product is evaluated as hi*hi + hi*lo + lo*hi on the tensor cores with fp32 accumulation;
+ * softmax statistics are fp32.  Head sizes other than 64 take a general fp32 SIMT kernel.
+ */
+#ifndef ATTN_SM100_H
+#define ATTN_SM100_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATTN_OK 0
+#define ATTN_ERR_NULL (-1)        /* a required pointer is NULL */
+#define ATTN_ERR_SHAPE (-2)       /* B, T, H or D is not positive, or an element count overflows */
+#define ATTN_ERR_UNSUPPORTED (-3) /* shape outside what any kernel handles (see attn_sm100_forward) */
+#define ATTN_ERR_ALIGN (-4)       /* a pointer is not 16-byte aligned */
+#define ATTN_ERR_DEVICE (-5)      /* current device is not an sm_100 GPU, or a driver entry point is missing */
+#define ATTN_ERR_KERNEL (-6)      /* reported by attn_sm100_device_status: a kernel gave up a bounded wait */
+
+/* flags */
+#define ATTN_FLAG_FORCE_GENERIC 1 /* use the general SIMT kernels even when the tensor-core path applies */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int attn_sm100_version(void);
+
+/*
+ * Prepares the current device: checks that it is compute capability 10.x, resolves the driver's
+ * tensor-map encoder, raises the dynamic shared-memory limit of the kernels and allocates the
+ * 4-byte device status word.  Idempotent; forward/backward call it on first use of a device, but
+ * that first call allocates, so call it yourself before timing or capturing anything.
+ */
+int attn_sm100_init(void);
+
+/*
+ * Size in bytes of the `saved` buffer that forward fills and backward reads: the bf16 hi/lo
+ * split of qkv, two planes of B*T*3C bf16 each, every plane padded to 256 bytes.
+ * Returns 0 for an invalid shape.
+ */
+size_t attn_sm100_saved_bytes(int B, int T, int H, int D);
+
+/*
+ * Size in bytes of the scratch buffer backward needs (bf16 hi/lo split of dout and one fp32 per
+ * (b, h, t) for rowsum(dout * out)).  Returns 0 for an invalid shape.
+ */
+size_t attn_sm100_backward_scratch_bytes(int B, int T, int H, int D);
+
+/*
+ * Forward.
+ *   qkv      [B, T, 3*H*D] fp32, read only
+ *   out      [B, T, H*D]   fp32, written
+ *   out_copy [B, T, H*D]   fp32, written with the same values when not NULL (the layer keeps it
+ *                          for backward because the caller's `out` is consumed by the next layer)
+ *   lse      [B, H, T]     fp32, written: log(sum_j exp(s_ij)) of the scaled scores
+ *   saved    attn_sm100_saved_bytes() bytes, written; must stay intact until backward has run
+ * D == 64 runs the tcgen05 tensor-core kernel for any T >= 1.  Other D run the general kernel,
+ * which needs D <= 256 and T <= 8192; larger values return ATTN_ERR_UNSUPPORTED.
+ */
+int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse, void *saved,
+                       int B, int T, int H, int D, int flags, void *stream);
+
+/*
+ * Backward.
+ *   saved    what forward wrote for the same qkv
+ *   out, lse what forward wrote (out may be the out_copy)
+ *   dout     [B, T, H*D]   fp32, read only
+ *   dqkv     [B, T, 3*H*D] fp32, every element written ([dq | dk | dv] per token); it does not
+ *                          need to be zeroed by the caller
+ *   scratch  attn_sm100_backward_scratch_bytes() bytes, clobbered
+ */
+int attn_sm100_backward(const void *saved, const float *out, const float *lse, const float *dout,
+                        float *dqkv, void *scratch, int B, int T, int H, int D, int flags, void *stream);
+
+/*
+ * Synchronises the current device and reads its status word.  *status receives 0, or a code
+ * >= 1000 naming the bounded wait that ran out inside a kernel.  When `clear` is non-zero the
+ * word is reset.  Returns ATTN_OK, ATTN_ERR_KERNEL when *status != 0, or a cudaError_t.
+ */
+int attn_sm100_device_status(int *status, int clear);
+
+/* Human-readable text for a return value of this library (static storage). */
+const char *attn_sm100_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ATTN_SM100_H */

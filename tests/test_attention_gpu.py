@@ -1,0 +1,236 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the golden
+vectors made from the reference.
+
+Tolerances (max-abs, the contract of this path): 2e-3 on the output, 5e-3 on dq/dk/dv.  The
+bf16 hi/lo precision recipe is expected to be far inside that; EXPECT_* are regression bounds for
+the recipe itself, so an accidental loss of a correction term is caught even while the contract
+tolerance would still pass.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TOL_OUT, TOL_DX = 2e-3, 5e-3
+EXPECT_OUT, EXPECT_DX = 2e-4, 5e-4
+GENERIC_TOL = 1e-4  # fp32 SIMT kernels (backward reads the 16-bit hi+lo copy of qkv)
+
+
+@pytest.fixture(scope="module")
+def gpu(pkg):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.cuda.set_device(0)
+    pkg.init()
+    return torch
+
+
+def run_cuda(pkg, torch, x, dout, H, flags=0):
+    """forward + backward through the C ABI; returns numpy out, lse, dx."""
+    xt = torch.from_numpy(x).cuda()
+    out, ctx = pkg.forward(xt, H, flags=flags, keep_copy=True)
+    dx = pkg.backward(ctx, torch.from_numpy(dout).cuda()) if dout is not None else None
+    assert pkg.device_status() == 0, "a kernel gave up a bounded wait"
+    assert torch.equal(out, ctx.out), "out and out_copy differ"
+    return out.cpu().numpy(), ctx.lse.cpu().numpy(), None if dx is None else dx.cpu().numpy()
+
+
+def seeded(seed, B, T, H, D):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((B, T, 3 * H * D), dtype=np.float32),
+            rng.standard_normal((B, T, H * D), dtype=np.float32))
+
+
+# ---------------------------------------------------------------------------------------------
+# general SIMT kernels
+# ---------------------------------------------------------------------------------------------
+def test_generic_reference_own_test_case(pkg, gpu):
+    z = np.load(os.path.join(GOLDEN, "ref_selfattn_case.npz"))
+    out, _, dx = run_cuda(pkg, gpu, z["qkv"], z["dout"], int(z["n_heads"]))
+    assert np.abs(out - z["out_model_py"]).max() < GENERIC_TOL
+    assert np.abs(dx - z["dqkv_model_py"]).max() < GENERIC_TOL
+    assert np.abs(out - z["out_cpu_kernel"]).max() < GENERIC_TOL
+    assert np.abs(dx - z["dqkv_cpu_kernel"]).max() < GENERIC_TOL
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "seeded_*.npz"))), ids=os.path.basename)
+def test_generic_golden(pkg, gpu, path):
+    z = np.load(path)
+    out, _, dx = run_cuda(pkg, gpu, z["x"], z["dout"], int(z["n_heads"]), flags=pkg.FLAG_FORCE_GENERIC)
+    assert np.abs(out - z["out"]).max() < GENERIC_TOL
+    assert np.abs(dx - z["dx"]).max() < GENERIC_TOL
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 2, 64), (1, 77, 3, 5), (2, 16, 1, 256), (1, 1024, 1, 32)])
+def test_generic_vs_oracle(pkg, gpu, oracle, shape):
+    B, T, H, D = shape
+    x, g = seeded(21, B, T, H, D)
+    out, lse, dx = run_cuda(pkg, gpu, x, g, H, flags=pkg.FLAG_FORCE_GENERIC)
+    ref_out, ref_lse = oracle.forward(x, H, want_lse=True)
+    assert np.abs(out - ref_out).max() < GENERIC_TOL
+    assert np.abs(lse - ref_lse).max() < GENERIC_TOL
+    assert np.abs(dx - oracle.backward(x, g, H)).max() < GENERIC_TOL
+
+
+# ---------------------------------------------------------------------------------------------
+# tensor-core kernels (D = 64)
+# ---------------------------------------------------------------------------------------------
+FAST_SHAPES = [
+    (1, 128, 1), (1, 1, 1), (2, 2, 2), (1, 127, 1), (1, 129, 2), (2, 130, 2), (1, 256, 1), (2, 200, 3),
+    (1, 384, 2), (1, 1024, 2), (3, 640, 1), (8, 128, 12),
+]
+
+
+@pytest.mark.parametrize("shape", FAST_SHAPES, ids=lambda s: "B%d_T%d_H%d" % s)
+def test_fast_forward_vs_oracle(pkg, gpu, oracle, shape):
+    B, T, H = shape
+    x, _ = seeded(31, B, T, H, 64)
+    out, lse, _ = run_cuda(pkg, gpu, x, None, H)
+    ref_out, ref_lse = oracle.forward(x, H, want_lse=True)
+    err = np.abs(out - ref_out).max()
+    print("fwd", shape, "max|out-oracle| = %.3e, max|lse-oracle| = %.3e" % (err, np.abs(lse - ref_lse).max()))
+    assert err < TOL_OUT
+    assert err < EXPECT_OUT
+    assert np.abs(lse - ref_lse).max() < 1e-4
+
+
+@pytest.mark.parametrize("shape", FAST_SHAPES, ids=lambda s: "B%d_T%d_H%d" % s)
+def test_fast_backward_vs_oracle(pkg, gpu, oracle, shape):
+    B, T, H = shape
+    x, g = seeded(32, B, T, H, 64)
+    _, _, dx = run_cuda(pkg, gpu, x, g, H)
+    ref = oracle.backward(x, g, H)
+    C = H * 64
+    errs = [np.abs(dx[..., i * C:(i + 1) * C] - ref[..., i * C:(i + 1) * C]).max() for i in range(3)]
+    print("bwd", shape, "max-abs dq %.3e dk %.3e dv %.3e" % tuple(errs))
+    assert max(errs) < TOL_DX
+    assert max(errs) < EXPECT_DX
+
+
+@pytest.mark.parametrize("name", ["seeded_t130_d64", "seeded_t256_d64", "seeded_t1_d64"])
+def test_fast_golden(pkg, gpu, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    out, _, dx = run_cuda(pkg, gpu, z["x"], z["dout"], int(z["n_heads"]))
+    assert np.abs(out - z["out"]).max() < TOL_OUT
+    assert np.abs(dx - z["dx"]).max() < TOL_DX
+
+
+def test_fast_config1_digest(pkg, gpu):
+    """B=8, T=128, H=12, D=64 with seed 1234 against the digest of the reference CPU kernel."""
+    from tests.golden.make_golden import digest, seeded_inputs
+
+    z = np.load(os.path.join(GOLDEN, "config1_digest.npz"))
+    B, T, H, D = (int(v) for v in z["shape"])
+    x, dout = seeded_inputs(int(z["seed"]), B, T, H, D)
+    if abs(float(x.astype(np.float64).sum()) - float(z["x_sum"])) > 1e-6:
+        pytest.skip("numpy generator stream differs from the one the fixture was made with")
+    out, _, dx = run_cuda(pkg, gpu, x, dout, H)
+    so, s1, _ = digest(out)
+    sx, d1, _ = digest(dx)
+    assert np.abs(so - z["out_samples"]).max() < TOL_OUT
+    assert np.abs(sx - z["dx_samples"]).max() < TOL_DX
+    assert abs(s1 - float(z["out_sum"])) < 1.0 and abs(d1 - float(z["dx_sum"])) < 1.0
+
+
+def test_fast_matches_generic_on_gpu(pkg, gpu):
+    x, g = seeded(33, 2, 333, 2, 64)
+    o1, l1, d1 = run_cuda(pkg, gpu, x, g, 2)
+    o2, l2, d2 = run_cuda(pkg, gpu, x, g, 2, flags=pkg.FLAG_FORCE_GENERIC)
+    assert np.abs(o1 - o2).max() < EXPECT_OUT
+    assert np.abs(l1 - l2).max() < 1e-4
+    assert np.abs(d1 - d2).max() < EXPECT_DX
+
+
+def test_forward_is_deterministic_and_stays_inside_its_buffers(pkg, gpu):
+    torch = gpu
+    B, T, H, D = 2, 200, 2, 64
+    x, _ = seeded(34, B, T, H, D)
+    xt = torch.from_numpy(x).cuda()
+    pad = 4096
+    n_out = B * T * H * D
+    results = []
+    for _ in range(2):
+        buf = torch.full((n_out + 2 * pad,), 1234.5, device="cuda", dtype=torch.float32)
+        lbuf = torch.full((B * H * T + 2 * pad,), 1234.5, device="cuda", dtype=torch.float32)
+        saved = torch.empty(pkg.saved_bytes(B, T, H, D), device="cuda", dtype=torch.uint8)
+        out = buf[pad:pad + n_out].view(B, T, H * D)
+        lse = lbuf[pad:pad + B * H * T].view(B, H, T)
+        pkg.forward_into(xt, out, None, lse, saved, H)
+        assert pkg.device_status() == 0
+        assert bool((buf[:pad] == 1234.5).all()) and bool((buf[pad + n_out:] == 1234.5).all())
+        assert bool((lbuf[:pad] == 1234.5).all()) and bool((lbuf[pad + B * H * T:] == 1234.5).all())
+        results.append((out.clone(), lse.clone()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+
+
+def test_causality_on_gpu(pkg, gpu):
+    x, _ = seeded(35, 1, 300, 2, 64)
+    o0, _, _ = run_cuda(pkg, gpu, x, None, 2)
+    x2 = x.copy()
+    x2[:, 150:, :] += 0.5
+    o1, _, _ = run_cuda(pkg, gpu, x2, None, 2)
+    assert np.array_equal(o0[:, :150], o1[:, :150])
+
+
+def test_backward_does_not_need_zeroed_output(pkg, gpu):
+    torch = gpu
+    B, T, H, D = 1, 260, 2, 64
+    x, g = seeded(36, B, T, H, D)
+    out, ctx = pkg.forward(torch.from_numpy(x).cuda(), H)
+    gt = torch.from_numpy(g).cuda()
+    scratch = torch.empty(pkg.backward_scratch_bytes(B, T, H, D), device="cuda", dtype=torch.uint8)
+    res = []
+    for fill in (0.0, 777.0):
+        dqkv = torch.full((B, T, 3 * H * D), fill, device="cuda", dtype=torch.float32)
+        pkg.backward_into(ctx.saved, ctx.out, ctx.lse, gt, dqkv, scratch, H)
+        assert pkg.device_status() == 0
+        res.append(dqkv.cpu().numpy())
+    assert np.abs(res[0] - res[1]).max() < 1e-4  # dq is accumulated with atomics: order may differ
+
+
+# ---------------------------------------------------------------------------------------------
+# full-size workload (B=8, T=1024, H=12, D=64): properties that do not need the oracle at
+# full size, plus an oracle comparison on a slice of the batch
+# ---------------------------------------------------------------------------------------------
+def test_full_size_properties(pkg, gpu, oracle):
+    torch = gpu
+    B, T, H, D = 8, 1024, 12, 64
+    x, g = seeded(1234, B, T, H, D)
+    xt, gt = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    out, ctx = pkg.forward(xt, H)
+    dx = pkg.backward(ctx, gt)
+    assert pkg.device_status() == 0
+
+    # (1) batch shards are independent: running batch 5 alone gives the same bits forward,
+    #     and the same dk/dv bits backward (dq goes through atomics: equal within rounding)
+    o5, c5 = pkg.forward(xt[5:6].contiguous(), H)
+    d5 = pkg.backward(c5, gt[5:6].contiguous())
+    assert torch.equal(o5[0], out[5])
+    C = H * D
+    assert torch.equal(d5[0, :, C:], dx[5, :, C:])
+    assert float((d5[0, :, :C] - dx[5, :, :C]).abs().max()) < 1e-4
+
+    # (2) backward is linear in dout
+    dx2 = pkg.backward(ctx, (2.0 * gt).contiguous())
+    assert float((dx2 - 2.0 * dx).abs().max()) < 1e-3
+
+    # (3) row 0 of every (b, h) attends only to itself: out = v_0, and dv gets all of dout there
+    v0 = xt[:, 0, 2 * C:]
+    assert float((out[:, 0, :] - v0).abs().max()) < 1e-4
+
+    # (4) a slice against the oracle (first and last batch entry)
+    sel = [0, B - 1]
+    xs, gs = x[sel], g[sel]
+    ref_o = oracle.forward(xs, H)
+    ref_d = oracle.backward(xs, gs, H)
+    e_o = np.abs(out[sel].cpu().numpy() - ref_o).max()
+    e_d = np.abs(dx[sel].cpu().numpy() - ref_d).max()
+    print("full-size slice: max|out| err %.3e, max|dqkv| err %.3e" % (e_o, e_d))
+    assert e_o < TOL_OUT and e_d < TOL_DX
+    assert e_o < EXPECT_OUT and e_d < EXPECT_DX
