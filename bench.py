@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the causal self-attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the attention layer over one batch of synthetic
+input.  The workload is the GPT-2 124M block shape the metric is quoted on: B=8, T=1024, H=12,
+D=64, fp32 in/out, qkv and dout i.i.d. N(0,1) from a fixed seed.  With N > 1 (launched through
+torch.distributed.run, one rank per GPU) every rank processes its own batch of 8 -- the (batch,
+head) units are independent, so there is no collective on the data path and scaling is weak.
+
+Printed JSON line (rank 0):
+  value      whole-job algorithmic TFLOP/s (6*B*H*T^2*D / 2 per pass, causal count) with inputs
+             resident in HBM, CUDA-event time, max over ranks
+  e2e        the same metric through the C ABI with pinned HOST buffers: the H2D copy of qkv and
+             dout and the D2H copy of out and dqkv are inside the timed region
+  roofline   the dominant kernel (backward core) timed live with CUDA events
+  cpu_baseline  the reference's own CPU attention (OpenBLAS) on this box's host cores, rank 0, N=1
+
+--impl reference times the reference's own CPU implementation of the path (compiled out of tree
+into oracle/_ref, else the plain-C port in oracle/) on the host cores, on a bounded sample per
+step, and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = {"B": 8, "T": 1024, "H": 12, "D": 64}
+SEED = 1234
+METRIC = "attn fwd+bwd TFLOP/s"
+UNIT = "TFLOP/s"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+ROTATE = 4  # buffer sets cycled through so that a set is evicted from L2 before it is reused
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the
+# bench workload, from the ncu capture summarised under profiles/ (None until captured)
+BWD_CORE_DRAM_BYTES = None
+
+
+def flops_fwd(B, T, H, D):
+    return 2.0 * B * H * T * T * D
+
+
+def flops_bwd(B, T, H, D):
+    return 4.0 * B * H * T * T * D
+
+
+def algorithmic_bytes(B, T, H, D):
+    C = H * D
+    return {"fwd": 16.0 * B * T * C + 4.0 * B * H * T, "bwd": 32.0 * B * T * C + 4.0 * B * H * T}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS if k in p} | {"source": "measured"}
+    return dict(FALLBACK_PEAKS) | {"source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:  # NVML missing: report nulls rather than fail the bench
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=1.0)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+def seeded_host_inputs(rank: int):
+    import numpy as np
+
+    B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    rng = np.random.default_rng(SEED + rank)
+    x = rng.standard_normal((B, T, 3 * H * D), dtype=np.float32)
+    g = rng.standard_normal((B, T, H * D), dtype=np.float32)
+    return x, g
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm and CPU baseline (host cores only)
+# ------------------------------------------------------------------------------------------------
+def cpu_attention_runner():
+    """Returns (kind, run(x, g, H) -> seconds, info)."""
+    from oracle import build as oracle_build
+    from oracle import oracle
+
+    cores = os.cpu_count() or 1
+    if oracle.have_reference():
+        def run(x, g, H):
+            t0 = time.perf_counter()
+            oracle.reference_run(x, g, H, threads=cores)
+            return time.perf_counter() - t0
+
+        info = oracle.reference_info()
+        return "reference", run, {"cores": cores, "blas": info["blas"]}
+    oracle_build.build_oracle()
+
+    def run(x, g, H):
+        t0 = time.perf_counter()
+        oracle.forward(x, H)
+        oracle.backward(x, g, H)
+        return time.perf_counter() - t0
+
+    return "port", run, {"cores": oracle.num_threads(), "blas": None}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # rank 0 alone measures the host cores
+    B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    sample_b = 2
+    x, g = seeded_host_inputs(0)
+    x, g = x[:sample_b].copy(), g[:sample_b].copy()
+    kind, run, info = cpu_attention_runner()
+    for _ in range(args.warmup):
+        run(x, g, H)
+    times = [run(x, g, H) for _ in range(args.steps)]
+    total = sum(times)
+    fl = (flops_fwd(sample_b, T, H, D) + flops_bwd(sample_b, T, H, D)) * args.steps
+    value = fl / total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "causal attention fwd+bwd B=8 T=1024 H=12 D=64 fp32 io", "sample_batch": sample_b,
+                   "seed": SEED},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": kind,
+                         "sample": f"{sample_b} of {B} batch entries per step, fwd+bwd, {args.steps} steps",
+                         "blas": info["blas"]},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measure_cpu_baseline():
+    B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    x, g = seeded_host_inputs(0)
+    kind, run, info = cpu_attention_runner()
+    secs = run(x, g, H)  # one full pass of the workload
+    fl = flops_fwd(B, T, H, D) + flops_bwd(B, T, H, D)
+    return {"value": fl / secs / 1e12, "unit": UNIT, "cores": info["cores"], "kind": kind,
+            "sample": f"one fwd+bwd pass of the full workload (B={B}), {secs:.2f} s", "blas": info["blas"]}
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    pkg = entry.load_package()
+    pkg.init()
+    B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    C = H * D
+    dev = torch.device("cuda", local_rank)
+    xh, gh = seeded_host_inputs(rank)
+    x_pin = torch.from_numpy(xh).pin_memory()
+    g_pin = torch.from_numpy(gh).pin_memory()
+    out_pin = torch.empty((B, T, C), dtype=torch.float32).pin_memory()
+    dx_pin = torch.empty((B, T, 3 * C), dtype=torch.float32).pin_memory()
+
+    sets = []
+    for _ in range(ROTATE):
+        sets.append({
+            "x": x_pin.to(dev), "g": g_pin.to(dev),
+            "out": torch.empty((B, T, C), device=dev), "lse": torch.empty((B, H, T), device=dev),
+            "saved": torch.empty(pkg.saved_bytes(B, T, H, D), device=dev, dtype=torch.uint8),
+            "scratch": torch.empty(pkg.backward_scratch_bytes(B, T, H, D), device=dev, dtype=torch.uint8),
+            "dx": torch.empty((B, T, 3 * C), device=dev),
+        })
+    set_bytes = sum(t.numel() * t.element_size() for t in sets[0].values())
+    stream = torch.cuda.current_stream()
+
+    def step(i, events=None):
+        s = sets[i % ROTATE]
+        if events is not None:
+            events[0].record(stream)
+        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_PREPARE_ONLY)
+        if events is not None:
+            events[1].record(stream)
+        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_CORE_ONLY)
+        if events is not None:
+            events[2].record(stream)
+        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_PREPARE_ONLY)
+        if events is not None:
+            events[3].record(stream)
+        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_CORE_ONLY)
+        if events is not None:
+            events[4].record(stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # clock ramp (untimed, not counted as warm-up): the GPU idles at a low clock
+    t_end = time.perf_counter() + (0.0 if args.no_ramp else 0.3)
+    i = 0
+    while time.perf_counter() < t_end:
+        step(i)
+        i += 1
+    torch.cuda.synchronize()
+
+    # ---------------- device-resident timed region ----------------
+    for i in range(args.warmup):
+        step(i)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    barrier()
+    sampler.start()
+    t0.record(stream)
+    for i in range(args.steps):
+        step(i, ev[i])
+    t1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(t0.elapsed_time(t1))
+    status = pkg.device_status()
+    if status != 0:
+        raise SystemExit(f"kernel status word {status}: a bounded wait ran out")
+    stage_ms = [statistics.mean(ev[i][k].elapsed_time(ev[i][k + 1]) for i in range(args.steps)) for k in range(4)]
+
+    # ---------------- end-to-end through the C ABI with host buffers ----------------
+    def e2e_step(i):
+        s = sets[i % ROTATE]
+        s["x"].copy_(x_pin, non_blocking=True)
+        s["g"].copy_(g_pin, non_blocking=True)
+        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H)
+        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H)
+        out_pin.copy_(s["out"], non_blocking=True)
+        dx_pin.copy_(s["dx"], non_blocking=True)
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+
+    flops_step = flops_fwd(B, T, H, D) + flops_bwd(B, T, H, D)
+    value = flops_step * world * args.steps / (ms_total * 1e-3) / 1e12
+    e2e_value = flops_step * world * args.steps / (e2e_ms * 1e-3) / 1e12
+    h2d = x_pin.numel() * 4 + g_pin.numel() * 4
+    d2h = out_pin.numel() * 4 + dx_pin.numel() * 4
+
+    peaks = load_peaks()
+    bwd_core_s = stage_ms[3] * 1e-3
+    achieved = flops_bwd(B, T, H, D) / bwd_core_s / 1e12
+    peak_tf = peaks["bf16_tflops_sustained"]
+    ab = algorithmic_bytes(B, T, H, D)
+    roofline = {
+        "kernel": "attn_bwd_kernel (backward core)", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
+        "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": BWD_CORE_DRAM_BYTES,
+        "peak_source": peaks["source"] + " (cuBLAS bf16, sustained)",
+        "launch_us": stage_ms[3] * 1e3,
+        "hbm": {"achieved_gbs": ab["bwd"] / bwd_core_s / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                "frac": ab["bwd"] / bwd_core_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": ab["bwd"]},
+    }
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline = measure_cpu_baseline()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": "causal attention fwd+bwd, fused qkv [B,T,3C] fp32 io, B=8 T=1024 H=12 D=64 per GPU",
+                "global_batch": B * world, "seq_len": T, "n_heads": H, "head_dim": D, "seed": SEED,
+                "precision": "bf16 hi/lo split operands (3 MMAs per product), fp32 accumulate and softmax",
+                "l2": f"{ROTATE} rotating buffer sets of {set_bytes / 1e6:.0f} MB each (> 126 MB L2 between reuses)",
+                "parallelism": f"batch shards on {world} GPU(s), no collective",
+            },
+            "pct_of_nominal_bf16_peak": 100.0 * value / (NOMINAL_BF16_TFLOPS * world),
+            "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops_sustained"] * world),
+            "stage_us": {"fwd_split": stage_ms[0] * 1e3, "fwd_core": stage_ms[1] * 1e3,
+                         "bwd_prepare": stage_ms[2] * 1e3, "bwd_core": stage_ms[3] * 1e3},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clocks,
+            "roofline": roofline,
+            "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    ap.add_argument("--no-ramp", action="store_true", help="skip the untimed clock ramp (for profiler captures)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20  # each step is ~a second of host work; keep the arm within minutes
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -20,6 +20,8 @@ LIB_PATH = os.path.join(HERE, "lib", "libattn_sm100.so")
 HEADER_PATH = os.path.join(HERE, "..", "include", "attn_sm100.h")
 
 FLAG_FORCE_GENERIC = 1
+FLAG_PREPARE_ONLY = 2
+FLAG_CORE_ONLY = 4
 
 # name -> (restype, argtypes); must list every function include/attn_sm100.h declares
 _c = ctypes

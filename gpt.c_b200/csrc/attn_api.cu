@@ -33,6 +33,8 @@ bool shape_ok(int B, int T, int H, int D) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+bool stages_ok(int flags) { return !((flags & ATTN_FLAG_PREPARE_ONLY) && (flags & ATTN_FLAG_CORE_ONLY)); }
+
 bool use_fast(int D, int flags) { return D == 64 && !(flags & ATTN_FLAG_FORCE_GENERIC); }
 
 // bf16 planes of a [B, T, W] tensor as a 4-D map {W, T, B, plane}, box {64, 128, 1, 1}.
@@ -111,7 +113,7 @@ size_t attn_sm100_backward_scratch_bytes(int B, int T, int H, int D) {
 int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse, void *saved, int B, int T, int H,
                        int D, int flags, void *stream) {
     if (!qkv || !out || !lse || !saved) return ATTN_ERR_NULL;
-    if (!shape_ok(B, T, H, D)) return ATTN_ERR_SHAPE;
+    if (!shape_ok(B, T, H, D) || !stages_ok(flags)) return ATTN_ERR_SHAPE;
     if (!aligned16(qkv) || !aligned16(out) || !aligned16(saved) || (out_copy && !aligned16(out_copy)))
         return ATTN_ERR_ALIGN;
     const bool fast = use_fast(D, flags);
@@ -125,8 +127,12 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
     const size_t plane = attn::plane_bytes(n);
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(saved);
     __nv_bfloat16 *lo = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(saved) + plane);
-    cudaError_t e = attn::launch_split(qkv, hi, lo, n, s);
-    if (e != cudaSuccess) return (int)e;
+    cudaError_t e = cudaSuccess;
+    if (!(flags & ATTN_FLAG_CORE_ONLY)) {
+        e = attn::launch_split(qkv, hi, lo, n, s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (flags & ATTN_FLAG_PREPARE_ONLY) return ATTN_OK;
 
     if (fast) {
         CUtensorMap map_x;
@@ -142,7 +148,7 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
 int attn_sm100_backward(const void *saved, const float *out, const float *lse, const float *dout, float *dqkv,
                         void *scratch, int B, int T, int H, int D, int flags, void *stream) {
     if (!saved || !out || !lse || !dout || !dqkv || !scratch) return ATTN_ERR_NULL;
-    if (!shape_ok(B, T, H, D)) return ATTN_ERR_SHAPE;
+    if (!shape_ok(B, T, H, D) || !stages_ok(flags)) return ATTN_ERR_SHAPE;
     if (!aligned16(saved) || !aligned16(out) || !aligned16(dout) || !aligned16(dqkv) || !aligned16(scratch))
         return ATTN_ERR_ALIGN;
     const bool fast = use_fast(D, flags);
@@ -160,10 +166,14 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
     __nv_bfloat16 *dlo = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(scratch) + oplane);
     float *delta = reinterpret_cast<float *>(static_cast<char *>(scratch) + 2 * oplane);
 
-    cudaError_t e;
+    cudaError_t e = cudaSuccess;
+    const bool prepare = !(flags & ATTN_FLAG_CORE_ONLY), core = !(flags & ATTN_FLAG_PREPARE_ONLY);
     if (fast) {
-        e = attn::launch_bwd_prepare(dout, out, delta, dhi, dlo, dqkv, B, T, H, D, s);
-        if (e != cudaSuccess) return (int)e;
+        if (prepare) {
+            e = attn::launch_bwd_prepare(dout, out, delta, dhi, dlo, dqkv, B, T, H, D, s);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (!core) return ATTN_OK;
         CUtensorMap map_x, map_do;
         rc = encode_planes(&map_x, saved, B, T, 3 * H * D, xplane);
         if (rc != 0) return rc;
@@ -171,8 +181,11 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
         if (rc != 0) return rc;
         e = attn::launch_fast_backward(map_x, map_do, lse, delta, dqkv, B, T, H, ds->status, s);
     } else {
-        e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, B, T, H, D, s);
-        if (e != cudaSuccess) return (int)e;
+        if (prepare) {
+            e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, B, T, H, D, s);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (!core) return ATTN_OK;
         e = attn::launch_generic_backward(xhi, xlo, lse, delta, dout, dqkv, B, T, H, D, s);
     }
     return (int)e;

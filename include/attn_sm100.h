@@ -63,6 +63,12 @@ extern "C" {
 
 /* flags */
 #define ATTN_FLAG_FORCE_GENERIC 1 /* use the general SIMT kernels even when the tensor-core path applies */
+/* forward and backward each enqueue a preparation kernel (the bf16 hi/lo split of qkv; the split
+ * of dout with rowsum(dout*out) and the zero-fill of dq) followed by the core attention kernel.
+ * These two flags enqueue only one of the two stages, e.g. to time them separately or to reuse a
+ * `saved` buffer that is already filled.  Setting both is an error (ATTN_ERR_SHAPE). */
+#define ATTN_FLAG_PREPARE_ONLY 2
+#define ATTN_FLAG_CORE_ONLY 4
 
 /* Library version: major * 10000 + minor * 100 + patch. */
 int attn_sm100_version(void);
