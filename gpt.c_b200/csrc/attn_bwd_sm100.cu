@@ -17,12 +17,15 @@
 // added into the (zeroed) dq third of the output with fp32 atomics, since other key tiles
 // contribute to the same rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
 //
-// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 tensor-memory
-// allocation, warps 4-7 compute (thread r <-> key r of the tile / query r for dQ).
+// Warp roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (the whole warp runs the
+// issue loop, one elected lane issues), warp 2 tensor-memory allocation, warps 4-19 compute.
+// A compute warp's quarter (warp % 4) selects the 32 tensor-memory lanes it may touch (keys for
+// S^T / dP^T / dK / dV, queries for dQ); its column group (0..3) selects 32 of the 128 query
+// columns of S^T / dP^T and 16 of the 64 columns of dQ / dK / dV.
 //
 // Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ0 [384,448)
-// dQ1 [448,512).  P^T and dS^T overwrite S^T and dP^T chunk by chunk: of each 32 columns the
-// first 16 take the packed hi parts and the last 16 the lo parts.
+// dQ1 [448,512).  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes
+// 8 columns of packed bf16 hi parts followed by 8 columns of packed lo parts.
 #include "attn_internal.h"
 #include "tc05.cuh"
 
@@ -34,7 +37,8 @@ using namespace tc05;
 constexpr int kTile = 128;
 constexpr int kD = 64;
 constexpr int kPlaneTile = kTile * kD * 2;  // 16 KiB
-constexpr int kThreads = 256;
+constexpr int kThreads = 640;
+constexpr int kComputeThreads = 512;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
 
@@ -88,7 +92,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         mbar_init(&sm.g_full, 1);
         mbar_init(&sm.g_empty, 1);
         mbar_init(&sm.st_full, 1);
-        mbar_init(&sm.pds_full, 128);
+        mbar_init(&sm.pds_full, kComputeThreads);
         mbar_init(&sm.dq_full[0], 1);
         mbar_init(&sm.dq_full[1], 1);
         mbar_init(&sm.row_bar, 128);
@@ -128,7 +132,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        {
             constexpr uint32_t idesc_st = idesc_bf16_f32(kTile, kTile, 0, 0);  // S^T, dP^T
             constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);     // dV, dK (A in TMEM)
             constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);     // dQ (A, B MN-major)
@@ -151,11 +155,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
                                        smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
 
-            bool ok = mbar_wait(&sm.kv_full, 0, ctx, SITE_KV_FULL);
+            bool ok = mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL);
             for (int n = 0; ok && n < niter; n++) {
                 const uint32_t par = n & 1;
-                if (!mbar_wait(&sm.q_full, par, ctx, SITE_Q_FULL)) break;
-                if (!mbar_wait(&sm.g_full, par, ctx, SITE_G_FULL)) break;
+                if (!mbar_wait_warp(&sm.q_full, par, ctx, SITE_Q_FULL)) break;
+                if (!mbar_wait_warp(&sm.g_full, par, ctx, SITE_G_FULL)) break;
                 tc_fence_after_sync();
                 uint32_t acc = 0;
 #pragma unroll
@@ -163,7 +167,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
                     for (int kk = 0; kk < kD / 16; kk++) {
-                        mma_ss(tmem + kColST, desc_advance(k_km[a], kk * 32), desc_advance(q_km[bb], kk * 32), idesc_st,
+                        mma_ss_elect(tmem + kColST, desc_advance(k_km[a], kk * 32), desc_advance(q_km[bb], kk * 32), idesc_st,
                                acc);
                         acc = 1;
                     }
@@ -174,14 +178,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
                     for (int kk = 0; kk < kD / 16; kk++) {
-                        mma_ss(tmem + kColDPT, desc_advance(v_km[a], kk * 32), desc_advance(g_km[bb], kk * 32),
+                        mma_ss_elect(tmem + kColDPT, desc_advance(v_km[a], kk * 32), desc_advance(g_km[bb], kk * 32),
                                idesc_st, acc);
                         acc = 1;
                     }
                 }
-                tc_commit(&sm.st_full);
+                tc_commit_elect(&sm.st_full);
 
-                if (!mbar_wait(&sm.pds_full, par, ctx, SITE_PDS_FULL)) break;
+                if (!mbar_wait_warp(&sm.pds_full, par, ctx, SITE_PDS_FULL)) break;
                 tc_fence_after_sync();
                 // dV += P^T dO_i
 #pragma unroll
@@ -189,24 +193,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; kk++) {
-                        const uint32_t a_t = tmem + kColST + 32 * (kk >> 1) + 16 * a + 8 * (kk & 1);
-                        mma_ts(tmem + kColDV, a_t, desc_advance(g_mn[bb], kk * 2048), idesc_kv,
+                        const uint32_t a_t = tmem + kColST + 16 * kk + 8 * a;
+                        mma_ts_elect(tmem + kColDV, a_t, desc_advance(g_mn[bb], kk * 2048), idesc_kv,
                                (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
-                tc_commit(&sm.g_empty);
+                tc_commit_elect(&sm.g_empty);
                 // dK += dS^T Q_i
 #pragma unroll
                 for (int term = 0; term < 3; term++) {
                     const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; kk++) {
-                        const uint32_t a_t = tmem + kColDPT + 32 * (kk >> 1) + 16 * a + 8 * (kk & 1);
-                        mma_ts(tmem + kColDK, a_t, desc_advance(q_mn[bb], kk * 2048), idesc_kv,
+                        const uint32_t a_t = tmem + kColDPT + 16 * kk + 8 * a;
+                        mma_ts_elect(tmem + kColDK, a_t, desc_advance(q_mn[bb], kk * 2048), idesc_kv,
                                (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
-                tc_commit(&sm.q_empty);
+                tc_commit_elect(&sm.q_empty);
                 // dQ_i = dS K_j
                 const uint32_t d_q = tmem + kColDQ + (n & 1) * kD;
 #pragma unroll
@@ -214,53 +218,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; kk++) {
-                        mma_ss(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048), idesc_dq,
+                        mma_ss_elect(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048), idesc_dq,
                                (term > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
-                tc_commit(&sm.dq_full[n & 1]);
+                tc_commit_elect(&sm.dq_full[n & 1]);
             }
         }
     } else if (warp >= 4) {
         // ------------------------------ compute group ------------------------------
-        const int row = ((warp & 3) << 5) | lane;  // key inside the tile == TMEM lane; query row for dQ
-        const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
-        const uint32_t t_st = tmem + lane_addr + kColST;
-        const uint32_t t_dpt = tmem + lane_addr + kColDPT;
+        const int quarter = warp & 3;
+        const int cq = (warp - 4) >> 2;           // column group: query columns [32cq, 32cq+32)
+        const int row = (quarter << 5) | lane;    // key inside the tile == TMEM lane; query row for dQ
+        const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
+        const uint32_t t_st = tmem + lane_addr + kColST + 32 * cq;
+        const uint32_t t_dpt = tmem + lane_addr + kColDPT + 32 * cq;
         bool ok = true;
 
-        // dQ of iteration n: wait for it, scale, add into the dq third of dqkv.
+        // dQ of iteration n: wait for it, scale, add this thread's 16 columns into dqkv.
         auto flush_dq = [&](int n, int site) -> bool {
             if (!mbar_wait_warp(&sm.dq_full[n & 1], (n >> 1) & 1, ctx, site)) return false;
             tc_fence_after_sync();
             const int t = (jt + n) * kTile + row;
-            float *dst = dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD;
+            uint32_t r[16];
+            tmem_ld16(tmem + lane_addr + kColDQ + (n & 1) * kD + 16 * cq, r);
+            tmem_wait_ld();
+            if (t < T) {
+                float4 *dst = reinterpret_cast<float4 *>(dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD + 16 * cq);
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_addr + kColDQ + (n & 1) * kD + 32 * c, r);
-                tmem_wait_ld();
-                if (t < T) {
-#pragma unroll
-                    for (int e = 0; e < 32; e++) atomicAdd(dst + 32 * c + e, __uint_as_float(r[e]) * scale);
-                }
+                for (int e = 0; e < 4; e++)
+                    atomicAdd(dst + e, make_float4(__uint_as_float(r[4 * e]) * scale, __uint_as_float(r[4 * e + 1]) * scale,
+                                                   __uint_as_float(r[4 * e + 2]) * scale,
+                                                   __uint_as_float(r[4 * e + 3]) * scale));
             }
             return true;
         };
 
+        const float2 sc2 = make_float2(scale_log2, scale_log2);
         for (int n = 0; n < niter; n++) {
             const int it = jt + n;
             const bool diag = (n == 0);
             const int lb = n & 1;
-            {
+            if (cq == 0) {  // one column group stages the tile's row statistics for everybody
                 const int t = it * kTile + row;
-                sm.lse2[lb][row] = t < T ? lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
-                sm.delta[lb][row] = t < T ? delta[(size_t)bh * T + t] : 0.f;
+                sm.lse2[lb][row] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
+                sm.delta[lb][row] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
+                mbar_arrive(&sm.row_bar);
             }
-            // every compute thread has published its row before anyone reads the tile's statistics
-            mbar_arrive(&sm.row_bar);
             if (!mbar_wait_warp(&sm.row_bar, n & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
-
             if (!mbar_wait_warp(&sm.st_full, n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
             // the dS^T tile in shared memory is free once the previous dQ MMA has finished
             if (n >= 1 && !mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
@@ -270,41 +275,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_after_sync();
 
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t s[32], dp[32];
-                tmem_ld32(t_st + 32 * c, s);
-                tmem_ld32(t_dpt + 32 * c, dp);
+            for (int sub = 0; sub < 2; sub++) {
+                uint32_t sv[16], dp[16];
+                tmem_ld16(t_st + 16 * sub, sv);
+                tmem_ld16(t_dpt + 16 * sub, dp);
                 tmem_wait_ld();
-                uint32_t ph[16], pl[16], dh[16], dl[16];
+                const int q_base = 32 * cq + 16 * sub;  // first query column of this run
+                uint32_t ph[8], pl[8], dh[8], dl[8];
 #pragma unroll
-                for (int e = 0; e < 16; e++) {
-                    const int q0 = 32 * c + 2 * e, q1 = q0 + 1;
-                    float p0 = ex2(fmaf(__uint_as_float(s[2 * e]), scale_log2, -sm.lse2[lb][q0]));
-                    float p1 = ex2(fmaf(__uint_as_float(s[2 * e + 1]), scale_log2, -sm.lse2[lb][q1]));
+                for (int e = 0; e < 8; e++) {
+                    const int q0 = q_base + 2 * e;
+                    const float2 nl = *reinterpret_cast<const float2 *>(&sm.lse2[lb][q0]);   // -lse * log2(e)
+                    const float2 nd = *reinterpret_cast<const float2 *>(&sm.delta[lb][q0]);  // -delta
+                    const float2 x = fma2(make_float2(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1])), sc2, nl);
+                    float2 p = make_float2(ex2(x.x), ex2(x.y));
                     if (diag) {  // causal: a query sees a key only when query >= key
-                        if (q0 < row) p0 = 0.f;
-                        if (q1 < row) p1 = 0.f;
+                        if (q0 < row) p.x = 0.f;
+                        if (q0 + 1 < row) p.y = 0.f;
                     }
-                    const float d0 = p0 * (__uint_as_float(dp[2 * e]) - sm.delta[lb][q0]);
-                    const float d1 = p1 * (__uint_as_float(dp[2 * e + 1]) - sm.delta[lb][q1]);
-                    split_bf16x2(p0, p1, ph[e], pl[e]);
-                    split_bf16x2(d0, d1, dh[e], dl[e]);
+                    const float2 d = mul2(p, add2(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), nd));
+                    split_bf16x2_packed(p, ph[e], pl[e]);
+                    split_bf16x2_packed(d, dh[e], dl[e]);
                 }
-                tmem_st16(t_st + 32 * c, ph);
-                tmem_st16(t_st + 32 * c + 16, pl);
-                tmem_st16(t_dpt + 32 * c, dh);
-                tmem_st16(t_dpt + 32 * c + 16, dl);
-                // dS^T row `row`, queries 32c .. 32c+31, into the 128-byte-swizzled MN-major tile:
-                // query half m = c / 2, 16-byte chunk index (4 * (c % 2) + g) ^ (row % 8).
-                uint8_t *base_h = sm.ds[0][c >> 1] + row * 128;
-                uint8_t *base_l = sm.ds[1][c >> 1] + row * 128;
+                tmem_st8(t_st + 16 * sub, ph);
+                tmem_st8(t_st + 16 * sub + 8, pl);
+                tmem_st8(t_dpt + 16 * sub, dh);
+                tmem_st8(t_dpt + 16 * sub + 8, dl);
+                // dS^T row `row`, queries q_base .. q_base+15, into the 128-byte-swizzled MN-major
+                // tile: query half m = cq / 2, 16-byte chunk (4 * (cq % 2) + 2 * sub + g) ^ (row % 8)
+                uint8_t *base_h = sm.ds[0][cq >> 1] + row * 128;
+                uint8_t *base_l = sm.ds[1][cq >> 1] + row * 128;
 #pragma unroll
-                for (int g4 = 0; g4 < 4; g4++) {
-                    const int chunk = ((4 * (c & 1) + g4) ^ (row & 7)) * 16;
+                for (int g2 = 0; g2 < 2; g2++) {
+                    const int chunk = ((4 * (cq & 1) + 2 * sub + g2) ^ (row & 7)) * 16;
                     *reinterpret_cast<uint4 *>(base_h + chunk) =
-                        make_uint4(dh[4 * g4], dh[4 * g4 + 1], dh[4 * g4 + 2], dh[4 * g4 + 3]);
+                        make_uint4(dh[4 * g2], dh[4 * g2 + 1], dh[4 * g2 + 2], dh[4 * g2 + 3]);
                     *reinterpret_cast<uint4 *>(base_l + chunk) =
-                        make_uint4(dl[4 * g4], dl[4 * g4 + 1], dl[4 * g4 + 2], dl[4 * g4 + 3]);
+                        make_uint4(dl[4 * g2], dl[4 * g2 + 1], dl[4 * g2 + 2], dl[4 * g2 + 3]);
                 }
             }
             tmem_wait_st();
@@ -318,24 +325,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (ok && flush_dq(niter - 1, SITE_DQ_FULL_LAST)) {
             // the last dQ commit also covers every dV / dK MMA
             const int t = jt * kTile + row;
-            float *dk_dst = dqkv + ((size_t)b * T + t) * C3 + C + (size_t)h * kD;
-            float *dv_dst = dk_dst + C;
+            uint32_t rk[16], rv[16];
+            tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
+            tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
+            tmem_wait_ld();
+            if (t < T) {
+                float *dk_dst = dqkv + ((size_t)b * T + t) * C3 + C + (size_t)h * kD + 16 * cq;
+                float *dv_dst = dk_dst + C;
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t rk[32], rv[32];
-                tmem_ld32(tmem + lane_addr + kColDK + 32 * c, rk);
-                tmem_ld32(tmem + lane_addr + kColDV + 32 * c, rv);
-                tmem_wait_ld();
-                if (t < T) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 4) {
-                        *reinterpret_cast<float4 *>(dk_dst + 32 * c + e) =
-                            make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
-                                        __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
-                        *reinterpret_cast<float4 *>(dv_dst + 32 * c + e) =
-                            make_float4(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1]), __uint_as_float(rv[e + 2]),
-                                        __uint_as_float(rv[e + 3]));
-                    }
+                for (int e = 0; e < 16; e += 4) {
+                    *reinterpret_cast<float4 *>(dk_dst + e) =
+                        make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
+                                    __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
+                    *reinterpret_cast<float4 *>(dv_dst + e) =
+                        make_float4(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1]), __uint_as_float(rv[e + 2]),
+                                    __uint_as_float(rv[e + 3]));
                 }
             }
         }

@@ -104,6 +104,55 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const float *__restric
 }
 
 // ---------------------------------------------------------------------------------------
+// backward preparation for head size 64 (the tensor-core path): the same work as above with
+// 8 consecutive elements per thread, so 8 lanes cover one (b, t, h) row of 64 values.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bwd_prepare64_kernel(const float *__restrict__ dout, const float *__restrict__ out,
+                                                             float *__restrict__ delta, __nv_bfloat16 *__restrict__ dhi,
+                                                             __nv_bfloat16 *__restrict__ dlo, float *__restrict__ dq_zero,
+                                                             int B, int T, int H) {
+    const int C = H * 64;
+    const size_t nvec = (size_t)B * T * C / 8;  // multiple of 8, so whole groups of 8 lanes stay together
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int lane = threadIdx.x & 31;
+    // the loop bound is warp-uniform (shuffles below need every lane); memory accesses are guarded
+    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v - lane < nvec; v += stride) {
+        const bool active = v < nvec;
+        const size_t bt = v / (C / 8);
+        const int c8 = (int)(v % (C / 8));
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 g0 = active ? __ldcs(reinterpret_cast<const float4 *>(dout) + 2 * v) : zero4;
+        const float4 g1 = active ? __ldcs(reinterpret_cast<const float4 *>(dout) + 2 * v + 1) : zero4;
+        const float4 o0 = active ? __ldcs(reinterpret_cast<const float4 *>(out) + 2 * v) : zero4;
+        const float4 o1 = active ? __ldcs(reinterpret_cast<const float4 *>(out) + 2 * v + 1) : zero4;
+        float acc = g0.x * o0.x + g0.y * o0.y + g0.z * o0.z + g0.w * o0.w + g1.x * o1.x + g1.y * o1.y + g1.z * o1.z +
+                    g1.w * o1.w;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        const float f[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint32_t hw[4], lw[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+            __nv_bfloat162 ll = __floats2bfloat162_rn(f[2 * k] - __low2float(hh), f[2 * k + 1] - __high2float(hh));
+            hw[k] = *reinterpret_cast<uint32_t *>(&hh);
+            lw[k] = *reinterpret_cast<uint32_t *>(&ll);
+        }
+        if (!active) continue;
+        reinterpret_cast<uint4 *>(dhi)[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        reinterpret_cast<uint4 *>(dlo)[v] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        float4 *z = reinterpret_cast<float4 *>(dq_zero + bt * 3 * C + (size_t)c8 * 8);
+        z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((c8 & 7) == 0) {
+            const int h = c8 >> 3, t = (int)(bt % T), b = (int)(bt / T);
+            delta[((size_t)b * H + h) * T + t] = acc;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // generic forward: one warp per query row (b, h, i)
 // shared memory per warp: T scores + D query values
 // ---------------------------------------------------------------------------------------
@@ -289,6 +338,13 @@ cudaError_t launch_split(const float *x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, s
 
 cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta, __nv_bfloat16 *dhi,
                                __nv_bfloat16 *dlo, float *dq_zero, int B, int T, int H, int D, cudaStream_t s) {
+    if (D == 64 && dhi && dlo && dq_zero) {
+        const size_t nvec = (size_t)B * T * H * 8;
+        size_t blocks = (nvec + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        bwd_prepare64_kernel<<<(unsigned)blocks, 256, 0, s>>>(dout, out, delta, dhi, dlo, dq_zero, B, T, H);
+        return cudaGetLastError();
+    }
     const size_t rows = (size_t)B * T * H;
     size_t blocks = (rows + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
