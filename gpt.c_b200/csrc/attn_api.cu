@@ -37,11 +37,11 @@ bool stages_ok(int flags) { return !((flags & ATTN_FLAG_PREPARE_ONLY) && (flags 
 
 bool use_fast(int D, int flags) { return D == 64 && !(flags & ATTN_FLAG_FORCE_GENERIC); }
 
-// bf16 planes of a [B, T, W] tensor as a 4-D map {W, T, B, plane}, box {64, 128, 1, 1}.
-int encode_planes(CUtensorMap *map, const void *base, int B, int T, int W, size_t plane_stride_bytes) {
+// bf16 planes of a [B, T, W] tensor as a 4-D map {W, T, B, plane}, box {64, box_rows, 1, 1}.
+int encode_planes(CUtensorMap *map, const void *base, int B, int T, int W, size_t plane_stride_bytes, int box_rows) {
     const cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)T, (cuuint64_t)B, 2};
     const cuuint64_t strides[3] = {(cuuint64_t)W * 2, (cuuint64_t)W * 2 * (cuuint64_t)T, (cuuint64_t)plane_stride_bytes};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box,
                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -136,7 +136,7 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
 
     if (fast) {
         CUtensorMap map_x;
-        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, plane);
+        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, plane, 128);
         if (rc != 0) return rc;
         e = attn::launch_fast_forward(map_x, out, out_copy, lse, B, T, H, ds->status, s);
     } else {
@@ -175,9 +175,9 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
         }
         if (!core) return ATTN_OK;
         CUtensorMap map_x, map_do;
-        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, xplane);
+        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, xplane, 64);
         if (rc != 0) return rc;
-        rc = encode_planes(&map_do, scratch, B, T, H * D, oplane);
+        rc = encode_planes(&map_do, scratch, B, T, H * D, oplane, 64);
         if (rc != 0) return rc;
         e = attn::launch_fast_backward(map_x, map_do, lse, delta, dqkv, B, T, H, ds->status, s);
     } else {

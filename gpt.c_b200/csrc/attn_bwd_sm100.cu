@@ -17,11 +17,17 @@
 // added into the (zeroed) dq third of the output with fp32 atomics, since other key tiles
 // contribute to the same rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
 //
+// Each query tile is processed as two halves of 64 queries (A, B) with their own barriers, so the
+// tensor cores and the compute warps overlap: while the compute warps turn S^T/dP^T of half B
+// into P^T/dS^T, the tensor cores already run dV/dK of half A, and the next tile's S^T of half A
+// can be issued as soon as its Q/dO half has landed and the columns it overwrites were consumed.
+//
 // Warp roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (the whole warp runs the
-// issue loop, one elected lane issues), warp 2 tensor-memory allocation, warps 4-19 compute.
-// A compute warp's quarter (warp % 4) selects the 32 tensor-memory lanes it may touch (keys for
-// S^T / dP^T / dK / dV, queries for dQ); its column group (0..3) selects 32 of the 128 query
-// columns of S^T / dP^T and 16 of the 64 columns of dQ / dK / dV.
+// issue loop, one elected lane issues; whichever task is ready goes first), warp 2 tensor-memory
+// allocation, warps 4-19 compute.  A compute warp's quarter (warp % 4) selects the 32
+// tensor-memory lanes it may touch (keys for S^T / dP^T / dK / dV, queries for dQ); its column
+// group (0..3) selects 16 of the 64 query columns of a half and 16 of the 64 columns of
+// dQ / dK / dV.
 //
 // Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ0 [384,448)
 // dQ1 [448,512).  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes
@@ -35,8 +41,10 @@ namespace {
 using namespace tc05;
 
 constexpr int kTile = 128;
+constexpr int kHalf = 64;
 constexpr int kD = 64;
-constexpr int kPlaneTile = kTile * kD * 2;  // 16 KiB
+constexpr int kPlaneTile = kTile * kD * 2;  // 16 KiB: one bf16 plane of a 128-row tile
+constexpr int kPlaneHalf = kHalf * kD * 2;  // 8 KiB
 constexpr int kThreads = 640;
 constexpr int kComputeThreads = 512;
 constexpr uint32_t kTmemCols = 512;
@@ -45,25 +53,87 @@ constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ
 struct __align__(1024) BwdSmem {
     uint8_t k[2][kPlaneTile];      // K_j   [plane]
     uint8_t v[2][kPlaneTile];      // V_j
-    uint8_t q[2][kPlaneTile];      // Q_i
+    uint8_t q[2][kPlaneTile];      // Q_i   (rows 0-63 = half A, 64-127 = half B)
     uint8_t g[2][kPlaneTile];      // dO_i
     uint8_t ds[2][2][kPlaneTile];  // dS^T  [plane][query half][128 keys x 64 queries]
-    float lse2[2][kTile];          // log-sum-exp of the query tile, in log2 units, double buffered
-    float delta[2][kTile];
-    uint64_t kv_full, q_full, q_empty, g_full, g_empty, st_full, pds_full, dq_full[2], row_bar;
+    float lse2[2][kTile];          // -log-sum-exp of the query tile in log2 units, double buffered
+    float delta[2][kTile];         // -rowsum(dO * O)
+    uint64_t kv_full;
+    uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];  // [half]
+    uint64_t st_full[2], pds_full[2];                       // [half]
+    uint64_t dq_full[2];                                    // [iteration parity]
+    uint64_t row_bar;
     uint32_t tmem_base;
     int abort_flag;
 };
 
 enum Site : int {
-    SITE_Q_EMPTY = 101, SITE_G_EMPTY, SITE_KV_FULL, SITE_Q_FULL, SITE_G_FULL, SITE_PDS_FULL, SITE_ST_FULL,
-    SITE_DQ_FULL_FREE, SITE_DQ_FULL_READ, SITE_DQ_FULL_LAST, SITE_ROW_BAR
+    SITE_Q_EMPTY = 101, SITE_G_EMPTY, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
+    SITE_MMA_IDLE
 };
+
+// Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
+#ifdef ATTN_TRACE
+__device__ long long g_bwd_trace[2 * 16 * 8];
+#define BWD_TRACE(cond, role, it, k)                                                              \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && (cond)) g_bwd_trace[((role) * 16 + (it)) * 8 + (k)] = clock64();  \
+    } while (0)
+#else
+#define BWD_TRACE(cond, role, it, k) \
+    do {                             \
+    } while (0)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// P^T and dS^T of 16 query columns starting at local query index q_base (thread = key `row`).
+// Reads S^T / dP^T from tensor memory, writes the packed hi/lo pairs back in place and leaves
+// the dS^T pairs in dh/dl for the shared-memory copy.
+__device__ __forceinline__ void compute_run(const BwdSmem &sm, uint32_t t_st, uint32_t t_dpt, int lb, int q_base, int row,
+                                            bool diag, float2 sc2, uint32_t (&dh)[8], uint32_t (&dl)[8]) {
+    uint32_t sv[16], dp[16];
+    tmem_ld16(t_st, sv);
+    tmem_ld16(t_dpt, dp);
+    tmem_wait_ld();
+    uint32_t ph[8], pl[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const int q0 = q_base + 2 * e;
+        const float2 nl = *reinterpret_cast<const float2 *>(&sm.lse2[lb][q0]);   // -lse * log2(e)
+        const float2 nd = *reinterpret_cast<const float2 *>(&sm.delta[lb][q0]);  // -delta
+        const float2 x = fma2(make_float2(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1])), sc2, nl);
+        float2 p = make_float2(ex2(x.x), ex2(x.y));
+        if (diag) {  // causal: a query sees a key only when query >= key
+            if (q0 < row) p.x = 0.f;
+            if (q0 + 1 < row) p.y = 0.f;
+        }
+        const float2 d = mul2(p, add2(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), nd));
+        split_bf16x2_packed(p, ph[e], pl[e]);
+        split_bf16x2_packed(d, dh[e], dl[e]);
+    }
+    tmem_st8(t_st, ph);
+    tmem_st8(t_st + 8, pl);
+    tmem_st8(t_dpt, dh);
+    tmem_st8(t_dpt + 8, dl);
+}
+
+// dS^T row `row`, 16 queries of column group cq, into the 128-byte-swizzled MN-major tile of one
+// query half: 16-byte chunk index (2 * cq + g) ^ (row % 8).
+__device__ __forceinline__ void store_ds(uint8_t *tile_h, uint8_t *tile_l, int row, int cq, const uint32_t (&dh)[8],
+                                         const uint32_t (&dl)[8]) {
+#pragma unroll
+    for (int g2 = 0; g2 < 2; g2++) {
+        const int chunk = ((2 * cq + g2) ^ (row & 7)) * 16;
+        *reinterpret_cast<uint4 *>(tile_h + row * 128 + chunk) =
+            make_uint4(dh[4 * g2], dh[4 * g2 + 1], dh[4 * g2 + 2], dh[4 * g2 + 3]);
+        *reinterpret_cast<uint4 *>(tile_l + row * 128 + chunk) =
+            make_uint4(dl[4 * g2], dl[4 * g2 + 1], dl[4 * g2 + 2], dl[4 * g2 + 3]);
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -87,14 +157,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
         mbar_init(&sm.kv_full, 1);
-        mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.q_empty, 1);
-        mbar_init(&sm.g_full, 1);
-        mbar_init(&sm.g_empty, 1);
-        mbar_init(&sm.st_full, 1);
-        mbar_init(&sm.pds_full, kComputeThreads);
-        mbar_init(&sm.dq_full[0], 1);
-        mbar_init(&sm.dq_full[1], 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&sm.q_full[i], 1);
+            mbar_init(&sm.q_empty[i], 1);
+            mbar_init(&sm.g_full[i], 1);
+            mbar_init(&sm.g_empty[i], 1);
+            mbar_init(&sm.st_full[i], 1);
+            mbar_init(&sm.pds_full[i], kComputeThreads);
+            mbar_init(&sm.dq_full[i], 1);
+        }
         mbar_init(&sm.row_bar, 128);
         fence_barrier_init();
     }
@@ -108,136 +179,170 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const uint32_t tmem = sm.tmem_base;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ TMA producer (boxes of 64 rows) ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_x);
             tma_prefetch_desc(&map_do);
             const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
             mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
-            tma_load_4d(sm.k[0], &map_x, &sm.kv_full, xk, jt * kTile, b, 0);
-            tma_load_4d(sm.k[1], &map_x, &sm.kv_full, xk, jt * kTile, b, 1);
-            tma_load_4d(sm.v[0], &map_x, &sm.kv_full, xv, jt * kTile, b, 0);
-            tma_load_4d(sm.v[1], &map_x, &sm.kv_full, xv, jt * kTile, b, 1);
-            for (int n = 0; n < niter; n++) {
-                const int y = (jt + n) * kTile;
-                if (n >= 1 && !mbar_wait(&sm.q_empty, (n - 1) & 1, ctx, SITE_Q_EMPTY)) break;
-                mbar_expect_tx(&sm.q_full, 2 * kPlaneTile);
-                tma_load_4d(sm.q[0], &map_x, &sm.q_full, xq, y, b, 0);
-                tma_load_4d(sm.q[1], &map_x, &sm.q_full, xq, y, b, 1);
-                if (n >= 1 && !mbar_wait(&sm.g_empty, (n - 1) & 1, ctx, SITE_G_EMPTY)) break;
-                mbar_expect_tx(&sm.g_full, 2 * kPlaneTile);
-                tma_load_4d(sm.g[0], &map_do, &sm.g_full, h * kD, y, b, 0);
-                tma_load_4d(sm.g[1], &map_do, &sm.g_full, h * kD, y, b, 1);
+            for (int hf = 0; hf < 2; hf++) {
+                for (int pl = 0; pl < 2; pl++) {
+                    tma_load_4d(sm.k[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xk, jt * kTile + hf * kHalf, b, pl);
+                    tma_load_4d(sm.v[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xv, jt * kTile + hf * kHalf, b, pl);
+                }
+            }
+            bool ok = true;
+            for (int n = 0; ok && n < niter; n++) {
+                // the halves are released in the order dO_A, Q_A, dO_B, Q_B
+                for (int hf = 0; ok && hf < 2; hf++) {
+                    const int y = (jt + n) * kTile + hf * kHalf;
+                    if (n >= 1 && !mbar_wait(&sm.g_empty[hf], (n - 1) & 1, ctx, SITE_G_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(&sm.g_full[hf], 2 * kPlaneHalf);
+                    tma_load_4d(sm.g[0] + hf * kPlaneHalf, &map_do, &sm.g_full[hf], h * kD, y, b, 0);
+                    tma_load_4d(sm.g[1] + hf * kPlaneHalf, &map_do, &sm.g_full[hf], h * kD, y, b, 1);
+                    if (n >= 1 && !mbar_wait(&sm.q_empty[hf], (n - 1) & 1, ctx, SITE_Q_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(&sm.q_full[hf], 2 * kPlaneHalf);
+                    tma_load_4d(sm.q[0] + hf * kPlaneHalf, &map_x, &sm.q_full[hf], xq, y, b, 0);
+                    tma_load_4d(sm.q[1] + hf * kPlaneHalf, &map_x, &sm.q_full[hf], xq, y, b, 1);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        {
-            constexpr uint32_t idesc_st = idesc_bf16_f32(kTile, kTile, 0, 0);  // S^T, dP^T
-            constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);     // dV, dK (A in TMEM)
-            constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);     // dQ (A, B MN-major)
-            // K-major views (rows of 64 head-dim values)
-            const uint64_t k_km[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 16, 1024),
-                                      smem_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
-            const uint64_t v_km[2] = {smem_desc_sw128(smem_u32(sm.v[0]), 16, 1024),
-                                      smem_desc_sw128(smem_u32(sm.v[1]), 16, 1024)};
-            const uint64_t q_km[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 16, 1024),
-                                      smem_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
-            const uint64_t g_km[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 16, 1024),
-                                      smem_desc_sw128(smem_u32(sm.g[1]), 16, 1024)};
-            // MN-major views of the same bytes (the row index is the contraction index)
-            const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024),
-                                      smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
-            const uint64_t q_mn[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 1024, 1024),
-                                      smem_desc_sw128(smem_u32(sm.q[1]), 1024, 1024)};
-            const uint64_t g_mn[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 1024, 1024),
-                                      smem_desc_sw128(smem_u32(sm.g[1]), 1024, 1024)};
-            const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
-                                       smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
+        constexpr uint32_t idesc_st = idesc_bf16_f32(kTile, kHalf, 0, 0);  // S^T, dP^T of one half (N = 64)
+        constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);     // dV, dK (A in TMEM)
+        constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);     // dQ (A, B MN-major)
+        // K-major views (rows of 64 head-dim values)
+        const uint64_t k_km[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
+        const uint64_t v_km[2] = {smem_desc_sw128(smem_u32(sm.v[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.v[1]), 16, 1024)};
+        const uint64_t q_km[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
+        const uint64_t g_km[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.g[1]), 16, 1024)};
+        // MN-major views of the same bytes (the row index is the contraction index)
+        const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
+        const uint64_t q_mn[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.q[1]), 1024, 1024)};
+        const uint64_t g_mn[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.g[1]), 1024, 1024)};
+        const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
+                                   smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
 
-            bool ok = mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL);
-            for (int n = 0; ok && n < niter; n++) {
-                const uint32_t par = n & 1;
-                if (!mbar_wait_warp(&sm.q_full, par, ctx, SITE_Q_FULL)) break;
-                if (!mbar_wait_warp(&sm.g_full, par, ctx, SITE_G_FULL)) break;
-                tc_fence_after_sync();
-                uint32_t acc = 0;
+        bool ok = mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL);
+        // Two task streams, each in order: score tasks s = 2n + half (S^T, dP^T of one half) and
+        // gradient tasks g = 2n + half (dV, dK of one half; half B also issues dQ).  A score task may
+        // run once its Q/dO half has landed and the gradient task that read the columns it
+        // overwrites (g = s - 2) has been issued.  Score tasks have priority.
+        const int ntask = 2 * niter;
+        int s_idx = 0, g_idx = 0;
+        uint64_t idle_since = 0;
+        while (ok && g_idx < ntask) {
+            bool progressed = false;
+            if (s_idx < ntask && g_idx >= s_idx - 1) {
+                const int n = s_idx >> 1, hf = s_idx & 1;
+                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.q_full[hf], n & 1) && mbar_test_wait(&sm.g_full[hf], n & 1))) {
+                    tc_fence_after_sync();
+                    BWD_TRACE(lane == 0, 0, n, 0 + 4 * hf);
+                    uint32_t acc = 0;
 #pragma unroll
-                for (int term = 0; term < 3; term++) {
-                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                    for (int kk = 0; kk < kD / 16; kk++) {
-                        mma_ss_elect(tmem + kColST, desc_advance(k_km[a], kk * 32), desc_advance(q_km[bb], kk * 32), idesc_st,
-                               acc);
-                        acc = 1;
+                        for (int kk = 0; kk < kD / 16; kk++) {
+                            mma_ss_elect(tmem + kColST + hf * kHalf, desc_advance(k_km[a], kk * 32),
+                                         desc_advance(q_km[bb], hf * kPlaneHalf + kk * 32), idesc_st, acc);
+                            acc = 1;
+                        }
                     }
-                }
-                acc = 0;
+                    acc = 0;
 #pragma unroll
-                for (int term = 0; term < 3; term++) {
-                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                    for (int kk = 0; kk < kD / 16; kk++) {
-                        mma_ss_elect(tmem + kColDPT, desc_advance(v_km[a], kk * 32), desc_advance(g_km[bb], kk * 32),
-                               idesc_st, acc);
-                        acc = 1;
+                        for (int kk = 0; kk < kD / 16; kk++) {
+                            mma_ss_elect(tmem + kColDPT + hf * kHalf, desc_advance(v_km[a], kk * 32),
+                                         desc_advance(g_km[bb], hf * kPlaneHalf + kk * 32), idesc_st, acc);
+                            acc = 1;
+                        }
                     }
+                    tc_commit_elect(&sm.st_full[hf]);
+                    BWD_TRACE(lane == 0, 0, n, 1 + 4 * hf);
+                    s_idx++;
+                    progressed = true;
                 }
-                tc_commit_elect(&sm.st_full);
-
-                if (!mbar_wait_warp(&sm.pds_full, par, ctx, SITE_PDS_FULL)) break;
-                tc_fence_after_sync();
-                // dV += P^T dO_i
+            }
+            if (g_idx < s_idx) {
+                const int n = g_idx >> 1, hf = g_idx & 1;
+                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.pds_full[hf], n & 1))) {
+                    tc_fence_after_sync();
+                    BWD_TRACE(lane == 0, 0, n, 2 + 4 * hf);
+                    // dV += P^T dO_i over this half's 64 queries (4 K-steps of 16)
 #pragma unroll
-                for (int term = 0; term < 3; term++) {
-                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                    for (int kk = 0; kk < kTile / 16; kk++) {
-                        const uint32_t a_t = tmem + kColST + 16 * kk + 8 * a;
-                        mma_ts_elect(tmem + kColDV, a_t, desc_advance(g_mn[bb], kk * 2048), idesc_kv,
-                               (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            const int kk = 4 * hf + k4;
+                            mma_ts_elect(tmem + kColDV, tmem + kColST + 16 * kk + 8 * a, desc_advance(g_mn[bb], kk * 2048),
+                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                        }
                     }
-                }
-                tc_commit_elect(&sm.g_empty);
-                // dK += dS^T Q_i
+                    tc_commit_elect(&sm.g_empty[hf]);
+                    // dK += dS^T Q_i
 #pragma unroll
-                for (int term = 0; term < 3; term++) {
-                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                    for (int kk = 0; kk < kTile / 16; kk++) {
-                        const uint32_t a_t = tmem + kColDPT + 16 * kk + 8 * a;
-                        mma_ts_elect(tmem + kColDK, a_t, desc_advance(q_mn[bb], kk * 2048), idesc_kv,
-                               (n > 0 || term > 0 || kk > 0) ? 1u : 0u);
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            const int kk = 4 * hf + k4;
+                            mma_ts_elect(tmem + kColDK, tmem + kColDPT + 16 * kk + 8 * a, desc_advance(q_mn[bb], kk * 2048),
+                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                        }
                     }
-                }
-                tc_commit_elect(&sm.q_empty);
-                // dQ_i = dS K_j
-                const uint32_t d_q = tmem + kColDQ + (n & 1) * kD;
+                    tc_commit_elect(&sm.q_empty[hf]);
+                    if (hf == 1) {
+                        // dQ_i = dS K_j over all 128 keys; both halves of dS^T are in shared memory now
+                        const uint32_t d_q = tmem + kColDQ + (n & 1) * kD;
 #pragma unroll
-                for (int term = 0; term < 3; term++) {
-                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                        for (int term = 0; term < 3; term++) {
+                            const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                    for (int kk = 0; kk < kTile / 16; kk++) {
-                        mma_ss_elect(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048), idesc_dq,
-                               (term > 0 || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < kTile / 16; kk++) {
+                                mma_ss_elect(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048),
+                                             idesc_dq, (term > 0 || kk > 0) ? 1u : 0u);
+                            }
+                        }
+                        tc_commit_elect(&sm.dq_full[n & 1]);
                     }
+                    BWD_TRACE(lane == 0, 0, n, 3 + 4 * hf);
+                    g_idx++;
+                    progressed = true;
                 }
-                tc_commit_elect(&sm.dq_full[n & 1]);
+            }
+            if (progressed) {
+                idle_since = 0;
+            } else {  // bounded: give up when nothing became ready for a second
+                const uint64_t now = global_timer_ns();
+                if (idle_since == 0) idle_since = now;
+                const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
+                if (__any_sync(0xffffffffu, give_up)) {
+                    if (lane == 0 && !sm.abort_flag) {
+                        sm.abort_flag = 1;
+                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_MMA_IDLE);
+                    }
+                    ok = false;
+                }
             }
         }
     } else if (warp >= 4) {
         // ------------------------------ compute group ------------------------------
         const int quarter = warp & 3;
-        const int cq = (warp - 4) >> 2;           // column group: query columns [32cq, 32cq+32)
+        const int cq = (warp - 4) >> 2;           // column group: 16 query columns of each half
         const int row = (quarter << 5) | lane;    // key inside the tile == TMEM lane; query row for dQ
         const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
-        const uint32_t t_st = tmem + lane_addr + kColST + 32 * cq;
-        const uint32_t t_dpt = tmem + lane_addr + kColDPT + 32 * cq;
+        const uint32_t t_st = tmem + lane_addr + kColST + 16 * cq;
+        const uint32_t t_dpt = tmem + lane_addr + kColDPT + 16 * cq;
         bool ok = true;
 
-        // dQ of iteration n: wait for it, scale, add this thread's 16 columns into dqkv.
-        auto flush_dq = [&](int n, int site) -> bool {
-            if (!mbar_wait_warp(&sm.dq_full[n & 1], (n >> 1) & 1, ctx, site)) return false;
+        // dQ of iteration n (its barrier phase has been waited for): scale and add this thread's
+        // 16 columns into dqkv.
+        auto flush_dq = [&](int n) {
             tc_fence_after_sync();
             const int t = (jt + n) * kTile + row;
             uint32_t r[16];
@@ -251,7 +356,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                                                    __uint_as_float(r[4 * e + 2]) * scale,
                                                    __uint_as_float(r[4 * e + 3]) * scale));
             }
-            return true;
         };
 
         const float2 sc2 = make_float2(scale_log2, scale_log2);
@@ -266,63 +370,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 mbar_arrive(&sm.row_bar);
             }
             if (!mbar_wait_warp(&sm.row_bar, n & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
-            if (!mbar_wait_warp(&sm.st_full, n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+
+            uint32_t dh_a[8], dl_a[8], dh_b[8], dl_b[8];
+            // half A: queries 0..63 of the tile
+            BWD_TRACE(threadIdx.x == 128, 1, n, 0);
+            if (!mbar_wait_warp(&sm.st_full[0], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            BWD_TRACE(threadIdx.x == 128, 1, n, 1);
+            compute_run(sm, t_st, t_dpt, lb, 16 * cq, row, diag, sc2, dh_a, dl_a);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.pds_full[0]);  // dV / dK of half A may start; dS^T goes to shared memory below
+            BWD_TRACE(threadIdx.x == 128, 1, n, 2);
+            // half B: queries 64..127
+            if (!mbar_wait_warp(&sm.st_full[1], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            BWD_TRACE(threadIdx.x == 128, 1, n, 3);
+            compute_run(sm, t_st + kHalf, t_dpt + kHalf, lb, kHalf + 16 * cq, row, diag, sc2, dh_b, dl_b);
+            BWD_TRACE(threadIdx.x == 128, 1, n, 4);
             // the dS^T tile in shared memory is free once the previous dQ MMA has finished
             if (n >= 1 && !mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
                 ok = false;
                 break;
             }
-            tc_fence_after_sync();
-
-#pragma unroll
-            for (int sub = 0; sub < 2; sub++) {
-                uint32_t sv[16], dp[16];
-                tmem_ld16(t_st + 16 * sub, sv);
-                tmem_ld16(t_dpt + 16 * sub, dp);
-                tmem_wait_ld();
-                const int q_base = 32 * cq + 16 * sub;  // first query column of this run
-                uint32_t ph[8], pl[8], dh[8], dl[8];
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const int q0 = q_base + 2 * e;
-                    const float2 nl = *reinterpret_cast<const float2 *>(&sm.lse2[lb][q0]);   // -lse * log2(e)
-                    const float2 nd = *reinterpret_cast<const float2 *>(&sm.delta[lb][q0]);  // -delta
-                    const float2 x = fma2(make_float2(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1])), sc2, nl);
-                    float2 p = make_float2(ex2(x.x), ex2(x.y));
-                    if (diag) {  // causal: a query sees a key only when query >= key
-                        if (q0 < row) p.x = 0.f;
-                        if (q0 + 1 < row) p.y = 0.f;
-                    }
-                    const float2 d = mul2(p, add2(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), nd));
-                    split_bf16x2_packed(p, ph[e], pl[e]);
-                    split_bf16x2_packed(d, dh[e], dl[e]);
-                }
-                tmem_st8(t_st + 16 * sub, ph);
-                tmem_st8(t_st + 16 * sub + 8, pl);
-                tmem_st8(t_dpt + 16 * sub, dh);
-                tmem_st8(t_dpt + 16 * sub + 8, dl);
-                // dS^T row `row`, queries q_base .. q_base+15, into the 128-byte-swizzled MN-major
-                // tile: query half m = cq / 2, 16-byte chunk (4 * (cq % 2) + 2 * sub + g) ^ (row % 8)
-                uint8_t *base_h = sm.ds[0][cq >> 1] + row * 128;
-                uint8_t *base_l = sm.ds[1][cq >> 1] + row * 128;
-#pragma unroll
-                for (int g2 = 0; g2 < 2; g2++) {
-                    const int chunk = ((4 * (cq & 1) + 2 * sub + g2) ^ (row & 7)) * 16;
-                    *reinterpret_cast<uint4 *>(base_h + chunk) =
-                        make_uint4(dh[4 * g2], dh[4 * g2 + 1], dh[4 * g2 + 2], dh[4 * g2 + 3]);
-                    *reinterpret_cast<uint4 *>(base_l + chunk) =
-                        make_uint4(dl[4 * g2], dl[4 * g2 + 1], dl[4 * g2 + 2], dl[4 * g2 + 3]);
-                }
-            }
+            BWD_TRACE(threadIdx.x == 128, 1, n, 5);
+            store_ds(sm.ds[0][0], sm.ds[1][0], row, cq, dh_a, dl_a);
+            store_ds(sm.ds[0][1], sm.ds[1][1], row, cq, dh_b, dl_b);
             tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            mbar_arrive(&sm.pds_full);
+            mbar_arrive(&sm.pds_full[1]);
+            BWD_TRACE(threadIdx.x == 128, 1, n, 6);
 
-            if (n >= 1 && !flush_dq(n - 1, SITE_DQ_FULL_READ)) { ok = false; break; }
+            if (n >= 1) flush_dq(n - 1);
         }
 
-        if (ok && flush_dq(niter - 1, SITE_DQ_FULL_LAST)) {
+        if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {
+            flush_dq(niter - 1);
             // the last dQ commit also covers every dV / dK MMA
             const int t = jt * kTile + row;
             uint32_t rk[16], rv[16];
@@ -357,12 +441,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
 }  // namespace
 
+#ifdef ATTN_TRACE
+extern "C" int attn_bwd_trace_read(long long *dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_bwd_trace, sizeof(g_bwd_trace));
+}
+#endif
+
 static size_t bwd_smem_bytes() { return sizeof(BwdSmem) + 1024; }
 
 cudaError_t fast_bwd_set_attributes() {
     return cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem_bytes());
 }
 
+// map_x / map_do must have boxes of 64 rows (see the producer warp).
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const float *lse,
                                  const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s) {
     const int nt = (T + kTile - 1) / kTile;
