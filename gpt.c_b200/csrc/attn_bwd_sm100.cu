@@ -232,6 +232,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int ntask = 2 * niter;
         int s_idx = 0, g_idx = 0;
         uint64_t idle_since = 0;
+        uint32_t idle_polls = 0;
         while (ok && g_idx < ntask) {
             bool progressed = false;
             if (s_idx < ntask && g_idx >= s_idx - 1) {
@@ -316,10 +317,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
             }
             if (progressed) {
-                idle_since = 0;
-            } else {  // bounded: give up when nothing became ready for a second
+                idle_polls = 0;
+            } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up when nothing became ready for a second
                 const uint64_t now = global_timer_ns();
-                if (idle_since == 0) idle_since = now;
+                if (idle_polls == 256u) idle_since = now;
                 const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
                 if (__any_sync(0xffffffffu, give_up)) {
                     if (lane == 0 && !sm.abort_flag) {
@@ -351,23 +352,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (t < T) {
                 float4 *dst = reinterpret_cast<float4 *>(dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD + 16 * cq);
 #pragma unroll
-                for (int e = 0; e < 4; e++)
-                    atomicAdd(dst + e, make_float4(__uint_as_float(r[4 * e]) * scale, __uint_as_float(r[4 * e + 1]) * scale,
-                                                   __uint_as_float(r[4 * e + 2]) * scale,
-                                                   __uint_as_float(r[4 * e + 3]) * scale));
+                for (int e = 0; e < 4; e++)  // fire-and-forget vector reduction: nothing is returned
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e),
+                                 "f"(__uint_as_float(r[4 * e]) * scale), "f"(__uint_as_float(r[4 * e + 1]) * scale),
+                                 "f"(__uint_as_float(r[4 * e + 2]) * scale), "f"(__uint_as_float(r[4 * e + 3]) * scale)
+                                 : "memory");
             }
         };
 
         const float2 sc2 = make_float2(scale_log2, scale_log2);
+        if (cq == 0) {  // statistics of the first query tile
+            const int t = jt * kTile + row;
+            sm.lse2[0][row] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
+            sm.delta[0][row] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
+            mbar_arrive(&sm.row_bar);
+        }
         for (int n = 0; n < niter; n++) {
             const int it = jt + n;
             const bool diag = (n == 0);
             const int lb = n & 1;
-            if (cq == 0) {  // one column group stages the tile's row statistics for everybody
-                const int t = it * kTile + row;
-                sm.lse2[lb][row] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
-                sm.delta[lb][row] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
-                mbar_arrive(&sm.row_bar);
+            // Column group 0 stages the row statistics of every query tile for everybody, one tile
+            // ahead: the values of tile n+1 are fetched now and published after the wait on half B
+            // of this tile (by then nobody reads that buffer any more).
+            float next_lse = 0.f, next_delta = 0.f;  // raw loads; the arithmetic waits until they are published
+            if (cq == 0 && n + 1 < niter) {
+                const int t = (it + 1) * kTile + row;
+                if (t < T) {
+                    next_lse = lse[(size_t)bh * T + t];
+                    next_delta = delta[(size_t)bh * T + t];
+                }
             }
             if (!mbar_wait_warp(&sm.row_bar, n & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
 
@@ -382,17 +395,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_before_sync();
             mbar_arrive(&sm.pds_full[0]);  // dV / dK of half A may start; dS^T goes to shared memory below
             BWD_TRACE(threadIdx.x == 128, 1, n, 2);
+            // While the tensor cores work on half B's scores: the previous tile's dQ has finished by
+            // now, add it into the output.  That also frees the dS^T tile in shared memory.
+            if (n >= 1) {
+                if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
+                    ok = false;
+                    break;
+                }
+                flush_dq(n - 1);
+            }
+            BWD_TRACE(threadIdx.x == 128, 1, n, 7);
             // half B: queries 64..127
             if (!mbar_wait_warp(&sm.st_full[1], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
             tc_fence_after_sync();
+            if (cq == 0 && n + 1 < niter) {  // S^T of half B exists, so every thread is done with tile n-1
+                sm.lse2[lb ^ 1][row] = -next_lse * 1.4426950408889634f;
+                sm.delta[lb ^ 1][row] = -next_delta;
+                mbar_arrive(&sm.row_bar);
+            }
             BWD_TRACE(threadIdx.x == 128, 1, n, 3);
             compute_run(sm, t_st + kHalf, t_dpt + kHalf, lb, kHalf + 16 * cq, row, diag, sc2, dh_b, dl_b);
             BWD_TRACE(threadIdx.x == 128, 1, n, 4);
-            // the dS^T tile in shared memory is free once the previous dQ MMA has finished
-            if (n >= 1 && !mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
-                ok = false;
-                break;
-            }
             BWD_TRACE(threadIdx.x == 128, 1, n, 5);
             store_ds(sm.ds[0][0], sm.ds[1][0], row, cq, dh_a, dl_a);
             store_ds(sm.ds[0][1], sm.ds[1][1], row, cq, dh_b, dl_b);
@@ -401,8 +424,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_before_sync();
             mbar_arrive(&sm.pds_full[1]);
             BWD_TRACE(threadIdx.x == 128, 1, n, 6);
-
-            if (n >= 1) flush_dq(n - 1);
         }
 
         if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {

@@ -246,6 +246,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
             // is published and V_j has landed.  S has priority: the softmax groups wait on it.
             int next_qk = 0, next_pv = 0;
             uint64_t idle_since = 0;
+            uint32_t idle_polls = 0;
             while (ok && next_pv < ntiles) {
                 bool progressed = false;
                 if (next_qk < ntiles && next_qk - next_pv < kSBufs) {
@@ -303,10 +304,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
                     }
                 }
                 if (progressed) {
-                    idle_since = 0;
-                } else {  // bounded: give up when nothing became ready for a second
+                    idle_polls = 0;
+                } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up when nothing became ready for a second
                     const uint64_t now = global_timer_ns();
-                    if (idle_since == 0) idle_since = now;
+                    if (idle_polls == 256u) idle_since = now;
                     const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
                     if (__any_sync(0xffffffffu, give_up)) {
                         if (lane == 0 && !sm.abort_flag) {
