@@ -216,6 +216,8 @@ const char *attn_sm100_strerror(int code) {
         case ATTN_ERR_ALIGN: return "pointers must be 16-byte aligned";
         case ATTN_ERR_DEVICE: return "the current device is not an sm_100 GPU or a driver entry point is missing";
         case ATTN_ERR_KERNEL: return "a kernel gave up a bounded wait (see attn_sm100_device_status)";
+        case ATTN_ERR_STATIC_CAPACITY:
+            return "attn_sm100_forward_static: B*T*3*H*D exceeds the 4,194,304 elements the built-in scratch array holds";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -60,6 +60,7 @@ extern "C" {
 #define ATTN_ERR_ALIGN (-4)       /* a pointer is not 16-byte aligned */
 #define ATTN_ERR_DEVICE (-5)      /* current device is not an sm_100 GPU, or a driver entry point is missing */
 #define ATTN_ERR_KERNEL (-6)      /* reported by attn_sm100_device_status: a kernel gave up a bounded wait */
+#define ATTN_ERR_STATIC_CAPACITY (-7) /* attn_sm100_forward_static: the problem needs more than ATTN_STATIC_SCRATCH_BYTES */
 
 /* flags */
 #define ATTN_FLAG_FORCE_GENERIC 1 /* use the general SIMT kernels even when the tensor-core path applies */
@@ -119,6 +120,31 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
  */
 int attn_sm100_backward(const void *saved, const float *out, const float *lse, const float *dout,
                         float *dqkv, void *scratch, int B, int T, int H, int D, int flags, void *stream);
+
+/*
+ * Forward without any allocation.  (No counterpart in the reference: gpt.c allocates its caches with
+ * cudaMallocAsync on every call, kernels/src/cuda/Alloc.cu:9-14.)
+ *
+ * For callers that can neither pass a scratch buffer nor let the library enter the CUDA allocator:
+ * a server whose own pool owns all device memory, a latency-critical loop that must not risk the
+ * device-wide stall of a cudaMalloc, a host with a no-allocation-after-start-up rule.  The bf16 hi/lo
+ * split of qkv is kept in a fixed device array inside the library (ATTN_STATIC_SCRATCH_BYTES, held by
+ * every GPU that loads the library until the process exits) instead of a `saved` buffer, so the call
+ * is forward-only: there is nothing to hand to attn_sm100_backward.
+ *   qkv [B, T, 3*H*64] fp32 in, out [B, T, H*64] fp32, lse [B, H, T] fp32; D must be 64.
+ * Limits and rules
+ *   - 4 * B*T*3*H*D bytes (two bf16 planes, each padded to 256) must fit in ATTN_STATIC_SCRATCH_BYTES,
+ *     i.e. B*T*3*H*D <= 4,194,304 elements; larger problems return ATTN_ERR_STATIC_CAPACITY.
+ *   - No cudaMalloc / cudaFree / allocating library call is made, not even on first use.  The first
+ *     call on each device resolves the device address of the array (cudaGetSymbolAddress) and raises
+ *     the kernel's shared-memory limit; make that first call before starting any stream capture.
+ *   - All calls on a device share the array and it keeps the previous call's contents.  Each call
+ *     rewrites every byte it reads, so nothing needs clearing, but calls that overlap on the GPU
+ *     (other streams or threads) race on it: serialise them.
+ *   - Kernel status for this path is separate from attn_sm100_device_status.
+ */
+#define ATTN_STATIC_SCRATCH_BYTES (16u << 20)
+int attn_sm100_forward_static(const float *qkv, float *out, float *lse, int B, int T, int H, int D, void *stream);
 
 /*
  * Synchronises the current device and reads its status word.  *status receives 0, or a code
