@@ -136,7 +136,7 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
 
     if (fast) {
         CUtensorMap map_x;
-        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, plane, 128);
+        rc = encode_planes(&map_x, saved, B, T, 3 * H * D, plane, 64);
         if (rc != 0) return rc;
         e = attn::launch_fast_forward(map_x, out, out_copy, lse, B, T, H, ds->status, s);
     } else {

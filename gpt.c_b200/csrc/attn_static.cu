@@ -99,7 +99,7 @@ extern "C" int attn_sm100_forward_static(const float *qkv, float *out, float *ls
     const int W = 3 * H * D;
     const cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)T, (cuuint64_t)B, 2};
     const cuuint64_t strides[3] = {(cuuint64_t)W * 2, (cuuint64_t)W * 2 * (cuuint64_t)T, (cuuint64_t)plane};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t box[4] = {64, 64, 1, 1};  // the forward kernel loads 64-row boxes
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     if (g_encode_static(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, st.scratch, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
