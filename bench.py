@@ -44,7 +44,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 ROTATE = 4  # buffer sets cycled through so that a set is evicted from L2 before it is reused
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the
 # bench workload, from the ncu capture summarised under profiles/ (None until captured)
-BWD_CORE_DRAM_BYTES = None
+BWD_CORE_DRAM_BYTES = 190307840  # profiles/ncu_full_attention_B8_T1024_H12.txt
 
 
 def flops_fwd(B, T, H, D):
