@@ -63,3 +63,41 @@ def test_layer_forward_agrees_with_reference_cuda(tmp_path):
     o_new, _, _ = run_driver(OVERLAY, "cuda", x, g, 4, tmp_path)
     o_ref, _, _ = run_driver(REFERENCE, "cuda", x, g, 4, tmp_path)
     assert np.abs(o_new - o_ref).max() < 2e-2  # TF32 operands on the reference side
+
+
+TRAIN_OVERLAY = os.path.join(ROOT, "oracle", "_ref", "gptc_overlay", "train_gpt")
+TRAIN_REFERENCE = os.path.join(ROOT, "oracle", "_ref", "gptc_reference", "train_gpt")
+
+
+def _train_losses(exe, device, tmp_path, ckpt, tok, batch, block):
+    res = subprocess.run([exe, f"--train-data={tok}", "--max-epochs=1", f"--batch-size={batch}", f"--block-size={block}",
+                          f"--load-checkpoint={ckpt}", f"--device={device}", "--lr=3e-4",
+                          f"--log-dir={tmp_path}/logs_{device}"], capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-800:] + res.stderr[-800:]
+    import re
+
+    return [float(v) for v in re.findall(r"train loss: ([-\d.]+)", res.stdout)]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not (os.path.exists(TRAIN_OVERLAY) and os.path.exists(TRAIN_REFERENCE)),
+                    reason="train_gpt builds not present")
+def test_training_losses_match_reference_cpu_path(tmp_path):
+    """A small GPT-2 trained for a few steps by the unchanged train_gpt: the overlay build on the GPU
+    must follow the loss curve of the unmodified reference on its CPU path (the reference's CUDA
+    attention backward reads an uninitialised buffer, so it is not the yardstick)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "run_train_config", os.path.join(ROOT, "gpt.c_b200", "overlay", "run_train_config.py"))
+    rtc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rtc)
+    ckpt, tok = str(tmp_path / "ckpt.bin"), str(tmp_path / "tok.bin")
+    layers, heads, embd, batch, block, steps = 2, 2, 128, 2, 160, 5  # head size 64, ragged T
+    rtc.write_checkpoint(ckpt, layers, heads, embd, 50257, block, seed=7)
+    rtc.write_tokens(tok, steps, batch, block, 50257, seed=8)
+    cpu = _train_losses(TRAIN_REFERENCE, "cpu", tmp_path, ckpt, tok, batch, block)
+    gpu = _train_losses(TRAIN_OVERLAY, "cuda", tmp_path, ckpt, tok, batch, block)
+    assert len(cpu) == steps and len(gpu) == steps
+    # the Linear layers run TF32 cuBLAS on the GPU, so allow their rounding on a loss of about 10.8
+    assert max(abs(a - b) for a, b in zip(cpu, gpu)) < 5e-3
