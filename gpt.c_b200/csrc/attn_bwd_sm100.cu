@@ -79,7 +79,20 @@ __device__ long long g_bwd_trace[2 * 16 * 8];
     do {                                                                                          \
         if (blockIdx.x == 0 && (cond)) g_bwd_trace[((role) * 16 + (it)) * 8 + (k)] = clock64();  \
     } while (0)
+// life time of every 48th CTA in ns: rows 8..15 of role 1 are reused: [cta / 48][0..2]
+__device__ long long g_bwd_life[16 * 4];
+__device__ long long g_bwd_epi[8];
+#define BWD_EPI(k) do { if (blockIdx.x == 0 && threadIdx.x == 128) g_bwd_epi[k] = (long long)global_timer_ns(); } while (0)
+#define BWD_LIFE(k)                                                                          \
+    do {                                                                                     \
+        if (threadIdx.x == 128 && blockIdx.x % 48 == 0)                                      \
+            g_bwd_life[(blockIdx.x / 48) * 4 + (k)] = (long long)global_timer_ns();          \
+    } while (0)
 #else
+#define BWD_EPI(k) do {} while (0)
+#define BWD_LIFE(k) \
+    do {            \
+    } while (0)
 #define BWD_TRACE(cond, role, it, k) \
     do {                             \
     } while (0)
@@ -153,6 +166,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int niter = nt - jt;  // query tiles jt .. nt-1
 
     WaitCtx ctx{&sm.abort_flag, status};
+    BWD_LIFE(0);
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
@@ -349,7 +363,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             uint32_t r[16];
             tmem_ld16(tmem + lane_addr + kColDQ + (n & 1) * kD + 16 * cq, r);
             tmem_wait_ld();
+#ifdef ATTN_EXPERIMENT_NO_DQ
+            if (false) {
+#else
             if (t < T) {
+#endif
                 float4 *dst = reinterpret_cast<float4 *>(dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD + 16 * cq);
 #pragma unroll
                 for (int e = 0; e < 4; e++)  // fire-and-forget vector reduction: nothing is returned
@@ -360,6 +378,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
         };
 
+        BWD_LIFE(1);
         const float2 sc2 = make_float2(scale_log2, scale_log2);
         if (cq == 0) {  // statistics of the first query tile
             const int t = jt * kTile + row;
@@ -426,14 +445,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             BWD_TRACE(threadIdx.x == 128, 1, n, 6);
         }
 
+        BWD_LIFE(2);
+        BWD_EPI(0);
         if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {
+            BWD_EPI(1);
             flush_dq(niter - 1);
+            BWD_EPI(2);
             // the last dQ commit also covers every dV / dK MMA
             const int t = jt * kTile + row;
             uint32_t rk[16], rv[16];
             tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
             tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
             tmem_wait_ld();
+            BWD_EPI(3);
             if (t < T) {
                 float *dk_dst = dqkv + ((size_t)b * T + t) * C3 + C + (size_t)h * kD + 16 * cq;
                 float *dv_dst = dk_dst + C;
@@ -452,8 +476,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     // ------------------------------ tear-down ------------------------------
     if (sm.abort_flag) __nanosleep(50000);
+    BWD_EPI(4);
     tc_fence_before_sync();
     __syncthreads();
+    BWD_EPI(5);
+    BWD_LIFE(3);
     if (warp == 2) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);
@@ -465,6 +492,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #ifdef ATTN_TRACE
 extern "C" int attn_bwd_trace_read(long long *dst) {
     return (int)cudaMemcpyFromSymbol(dst, g_bwd_trace, sizeof(g_bwd_trace));
+}
+extern "C" int attn_bwd_epi_read(long long *dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_bwd_epi, sizeof(g_bwd_epi));
+}
+extern "C" int attn_bwd_life_read(long long *dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_bwd_life, sizeof(g_bwd_life));
 }
 #endif
 

@@ -15,7 +15,7 @@
 //
 // Warp roles (384 threads):
 //   warp 0       TMA producer for Q (once) and K (two-stage ring)
-//   warp 1       MMA issuer: S = Q K^T (SS, both K-major) and O += P V (P from tensor memory,
+//   warp 1       MMA issuer: S = Q K^T (Q from tensor memory, K K-major from shared memory) and O += P V (P from tensor memory,
 //                V MN-major from shared memory), each as hi*hi + hi*lo + lo*hi; the whole warp
 //                runs the loop, one elected lane issues
 //   warp 2       tensor-memory allocation / release
@@ -25,7 +25,8 @@
 //                score columns of a step and 32 of the 64 output columns; the halves exchange
 //                their row maximum through shared memory.
 //
-// Tensor memory (256 columns): S0 [0,64), S1 [64,128), O [128,192).  P overwrites S in place: each run of 16
+// Tensor memory (256 columns): S0 [0,64), S1 [64,128), O [128,192), Q hi/lo [192,256) (the A operand
+// of S = Q K^T, copied once from shared memory).  P overwrites S in place: each run of 16
 // score columns becomes 8 columns of packed bf16 hi parts followed by 8 columns of packed lo
 // parts.  O accumulates in tensor memory across key tiles (the PV MMAs accumulate); the running
 // reference maximum only moves when a row maximum exceeds it by more than 2^8, and only then is
@@ -46,13 +47,13 @@ constexpr int kPlaneStep = kStep * kD * 2;  // bytes of one bf16 plane of a K / 
 constexpr int kThreads = 384;
 constexpr int kSoftmaxThreads = 256;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 192;  // Q: hi plane [192,224), lo plane [224,256)
 
 struct __align__(1024) FwdSmem {
     uint8_t q[2][kPlaneTile];  // [plane]
     uint8_t k[2][2][kPlaneStep];  // [stage][plane]
     uint8_t v[2][2][kPlaneStep];
-    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t q_full, q_tmem, k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t s_full[2], p_full[2], o_full;
     uint64_t pair_bar[4];       // [quarter]: the two halves of a row block meet here once per tile
     float xmax[2][2][kTile];    // [tile parity][half][row]: row maxima exchanged between halves
@@ -63,7 +64,7 @@ struct __align__(1024) FwdSmem {
 
 enum Site : int {
     SITE_K_EMPTY = 1, SITE_V_EMPTY, SITE_Q_FULL, SITE_K_FULL, SITE_V_FULL, SITE_P_FULL, SITE_S_FULL, SITE_O_FULL,
-    SITE_O_FULL_LAST, SITE_PAIR
+    SITE_O_FULL_LAST, SITE_PAIR, SITE_Q_TMEM
 };
 
 // Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
@@ -73,7 +74,24 @@ __device__ long long g_fwd_trace[3 * 16 * 8];
     do {                                                                                            \
         if (blockIdx.x == 0 && (cond)) g_fwd_trace[((role) * 16 + (tile)) * 8 + (k)] = clock64();  \
     } while (0)
+// life time of every 48th CTA in ns: slot 2, [cta / 48][0..2] = start, set-up done, end
+#define FWD_LIFE(k)                                                                                         \
+    do {                                                                                                    \
+        if (threadIdx.x == 0 && blockIdx.x % 48 == 0)                                                       \
+            g_fwd_trace[(2 * 16 + blockIdx.x / 48) * 8 + (k)] = (long long)global_timer_ns();               \
+    } while (0)
+// phases of one light CTA (the last one) in ns: slot 1, row 15
+#define FWD_PHASE(cond, k)                                                                        \
+    do {                                                                                          \
+        if (blockIdx.x == gridDim.x - 1 && (cond)) g_fwd_trace[(1 * 16 + 15) * 8 + (k)] = (long long)global_timer_ns(); \
+    } while (0)
 #else
+#define FWD_PHASE(cond, k) \
+    do {                   \
+    } while (0)
+#define FWD_LIFE(k) \
+    do {            \
+    } while (0)
 #define FWD_TRACE(cond, role, tile, k) \
     do {                               \
     } while (0)
@@ -169,10 +187,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
     const int nsteps = 2 * (qt + 1);  // key steps of 64 up to the end of the diagonal tile
 
     WaitCtx ctx{&sm.abort_flag, status};
+    FWD_LIFE(0);
+    FWD_PHASE(threadIdx.x == 128, 0);
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
         mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_tmem, kSoftmaxThreads);
         for (int i = 0; i < 2; i++) {
             mbar_init(&sm.k_full[i], 1);
             mbar_init(&sm.k_empty[i], 1);
@@ -193,6 +214,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
+    FWD_LIFE(1);
 
     if (warp == 0) {
         // ------------------------------ TMA producer: Q, then K ------------------------------
@@ -228,8 +250,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         // ------------------------------ MMA issuer ------------------------------
         constexpr uint32_t idesc_s = idesc_bf16_f32(kTile, kStep, 0, 0);
         constexpr uint32_t idesc_o = idesc_bf16_f32(kTile, kD, 0, 1);
-        const uint64_t qd[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
-        bool ok = mbar_wait_warp(&sm.q_full, 0, ctx, SITE_Q_FULL);
+        // Q is the A operand of every S = Q K^T of this CTA: the softmax warps copy it once from
+        // shared to tensor memory, which halves the shared-memory traffic of those MMAs
+        bool ok = mbar_wait_warp(&sm.q_tmem, 0, ctx, SITE_Q_TMEM);
         // S of step j+1 is issued before the wait for P of step j: the two score buffers alternate,
         // so the tensor cores work on the next scores while the softmax warps are busy.  S_{j+1}
         // overwrites P_{j-1}; the tensor pipe runs in issue order, so PV_{j-1} has read it by then.
@@ -246,7 +269,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
                 const int qa = term == 2 ? 1 : 0, kb = term == 1 ? 1 : 0;  // hh, hl, lh
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; kk++) {
-                    mma_ss_elect(tmem + kColS + st * kStep, desc_advance(qd[qa], kk * 32), desc_advance(kd[kb], kk * 32),
+                    mma_ts_elect(tmem + kColS + st * kStep, tmem + kColQ + 32 * qa + 8 * kk, desc_advance(kd[kb], kk * 32),
                                  idesc_s, acc);
                     acc = 1;
                 }
@@ -292,6 +315,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         const uint32_t t_o = tmem + lane_addr + kColO + 32 * half;
 
         float m = -INFINITY, l = 0.f;
+
+        // copy this thread's Q row (half 0: hi plane, half 1: lo plane) from the swizzled shared
+        // memory tile into tensor memory: 64 bf16 = 32 packed columns, lane = row
+        if (mbar_wait_warp(&sm.q_full, 0, ctx, SITE_Q_FULL)) {
+            FWD_PHASE(threadIdx.x == 128, 1);
+            const uint8_t *qrow = sm.q[half] + row * 128;
+            uint32_t r[32];
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(qrow + ((c ^ (row & 7)) << 4));
+                r[4 * c] = v.x;
+                r[4 * c + 1] = v.y;
+                r[4 * c + 2] = v.z;
+                r[4 * c + 3] = v.w;
+            }
+            tmem_st32(tmem + lane_addr + kColQ + 32 * half, r);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.q_tmem);
+            FWD_PHASE(threadIdx.x == 128, 2);
+        }
         bool ok = true;
 
         for (int j = 0; j < nsteps; j++) {
@@ -303,6 +347,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
             if (!mbar_wait_warp(&sm.s_full[st], par, ctx, SITE_S_FULL)) { ok = false; break; }
             tc_fence_after_sync();
             FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 1);
+            if (j == 0) FWD_PHASE(threadIdx.x == 128, 3);
             float alpha;
             const bool step_ok = diag
                 ? max_pass<true>(sm, ctx, t_s, row, half, j & 1, key0, pair_bar, scale_log2, m, alpha)
@@ -329,6 +374,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
             tc_fence_before_sync();
             mbar_arrive(&sm.p_full[st]);
             FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 6);
+            if (j == nsteps - 1) FWD_PHASE(threadIdx.x == 128, 4);
         }
 
         // epilogue: O / l for this thread's 32 columns, log-sum-exp by the first half
@@ -336,6 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ok && mbar_wait_warp(&sm.o_full, (nsteps - 1) & 1, ctx, SITE_O_FULL_LAST)) {
             tc_fence_after_sync();
+            FWD_PHASE(threadIdx.x == 128, 5);
             uint32_t r[32];
             tmem_ld32(t_o, r);
             tmem_wait_ld();
@@ -366,6 +413,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);
     }
+    FWD_LIFE(2);
+    FWD_PHASE(threadIdx.x == 128, 6);
 }
 
 }  // namespace

@@ -372,11 +372,29 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 
 // hi/lo split of a pair with the residual computed as one packed fma: lo = bf16(p - float(hi)).
+// The hi part is rounded to nearest (|p - hi| <= 2^-9 |p|).  Float-to-bf16 conversions run on the
+// quarter-rate XU pipe together with exp2, which is the busiest pipe of the attention kernels, so
+// the lo part is taken by truncation on the integer pipe instead (byte permute of the two upper
+// halves): |p - hi - lo| < 2^-7 |p - hi| <= 2^-16 |p|.  TC05_SPLIT_MODE selects variants for
+// experiments: 0 = both parts rounded, 1 = lo truncated (default), 2 = both truncated (2^-14).
+#ifndef TC05_SPLIT_MODE
+#define TC05_SPLIT_MODE 1
+#endif
 __device__ __forceinline__ void split_bf16x2_packed(float2 p, uint32_t &hi, uint32_t &lo) {
+#if TC05_SPLIT_MODE == 2
+    hi = __byte_perm(__float_as_uint(p.x), __float_as_uint(p.y), 0x7632);
+    const float2 h = make_float2(__uint_as_float(__float_as_uint(p.x) & 0xFFFF0000u),
+                                 __uint_as_float(__float_as_uint(p.y) & 0xFFFF0000u));
+#else
     hi = pack_bf16x2(p.x, p.y);
     const float2 h = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xFFFF0000u));
+#endif
     const float2 r = fma2(h, make_float2(-1.f, -1.f), p);
+#if TC05_SPLIT_MODE == 0
     lo = pack_bf16x2(r.x, r.y);
+#else
+    lo = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x7632);
+#endif
 }
 
 }  // namespace tc05
