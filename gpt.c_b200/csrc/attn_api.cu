@@ -49,6 +49,18 @@ int encode_planes(CUtensorMap *map, const void *base, int B, int T, int W, size_
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// fp32 [B, T, W] tensor as a 3-D map {W, T, B}, box {32, 128, 1}: the output side of the backward kernel.
+int encode_rows_f32(CUtensorMap *map, const void *base, int B, int T, int W) {
+    const cuuint64_t dims[3] = {(cuuint64_t)W, (cuuint64_t)T, (cuuint64_t)B};
+    const cuuint64_t strides[2] = {(cuuint64_t)W * 4, (cuuint64_t)W * 4 * (cuuint64_t)T};
+    const cuuint32_t box[3] = {32, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 int current_device_state(DeviceState **out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -174,12 +186,14 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
             if (e != cudaSuccess) return (int)e;
         }
         if (!core) return ATTN_OK;
-        CUtensorMap map_x, map_do;
+        CUtensorMap map_x, map_do, map_dx;
         rc = encode_planes(&map_x, saved, B, T, 3 * H * D, xplane, 64);
         if (rc != 0) return rc;
         rc = encode_planes(&map_do, scratch, B, T, H * D, oplane, 64);
         if (rc != 0) return rc;
-        e = attn::launch_fast_backward(map_x, map_do, lse, delta, dqkv, B, T, H, ds->status, s);
+        rc = encode_rows_f32(&map_dx, dqkv, B, T, 3 * H * D);
+        if (rc != 0) return rc;
+        e = attn::launch_fast_backward(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, ds->status, s);
     } else {
         if (prepare) {
             e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, B, T, H, D, s);

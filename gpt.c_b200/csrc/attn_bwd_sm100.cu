@@ -56,12 +56,14 @@ struct __align__(1024) BwdSmem {
     uint8_t q[2][kPlaneTile];      // Q_i   (rows 0-63 = half A, 64-127 = half B)
     uint8_t g[2][kPlaneTile];      // dO_i
     uint8_t ds[2][2][kPlaneTile];  // dS^T  [plane][query half][128 keys x 64 queries]
+    uint8_t dqs[2][kPlaneTile];    // fp32 dQ tile on its way out: [32-column half][128 queries x 128 bytes]
     float lse2[2][kTile];          // -log-sum-exp of the query tile in log2 units, double buffered
     float delta[2][kTile];         // -rowsum(dO * O)
     uint64_t kv_full;
     uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];  // [half]
     uint64_t st_full[2], pds_full[2];                       // [half]
     uint64_t dq_full[2];                                    // [iteration parity]
+    uint64_t out_full, out_free;                            // staged output tile: written / read by the copy engine
     uint64_t row_bar;
     uint32_t tmem_base;
     int abort_flag;
@@ -69,7 +71,7 @@ struct __align__(1024) BwdSmem {
 
 enum Site : int {
     SITE_Q_EMPTY = 101, SITE_G_EMPTY, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
-    SITE_MMA_IDLE
+    SITE_MMA_IDLE, SITE_OUT_FULL, SITE_OUT_FREE, SITE_SMEM_ALIGN
 };
 
 // Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
@@ -151,10 +153,16 @@ __device__ __forceinline__ void store_ds(uint8_t *tile_h, uint8_t *tile_l, int r
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_do,
-                const float *__restrict__ lse, const float *__restrict__ delta, float *__restrict__ dqkv, int B, int T,
+                const __grid_constant__ CUtensorMap map_dx, const float *__restrict__ lse, const float *__restrict__ delta, float *__restrict__ dqkv, int B, int T,
                 int H, float scale, float scale_log2, int *status) {
-    extern __shared__ uint8_t smem_raw[];
-    BwdSmem &sm = *reinterpret_cast<BwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // The structure fills the whole 227 KiB, so there is no room to round the base up: the
+    // swizzled tiles need 1024-byte alignment and the kernel refuses to run without it.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    BwdSmem &sm = *reinterpret_cast<BwdSmem *>(smem_raw);
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_SMEM_ALIGN);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = B * H;
@@ -181,6 +189,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             mbar_init(&sm.dq_full[i], 1);
         }
         mbar_init(&sm.row_bar, 128);
+        mbar_init(&sm.out_full, kComputeThreads);
+        mbar_init(&sm.out_free, 1);
         fence_barrier_init();
     }
     if (warp == 2) {
@@ -355,27 +365,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint32_t t_dpt = tmem + lane_addr + kColDPT + 16 * cq;
         bool ok = true;
 
-        // dQ of iteration n (its barrier phase has been waited for): scale and add this thread's
-        // 16 columns into dqkv.
-        auto flush_dq = [&](int n) {
+        // One row (16 of its 64 columns) of an fp32 output tile into the staging layout the copy
+        // engine expects: two 32-column halves, 128-byte rows, 16-byte chunks swizzled by row % 8.
+        auto stage_row = [&](uint8_t *tile, const uint32_t (&r)[16], float f) {
+            uint8_t *base = tile + (cq >> 1) * kPlaneTile + row * 128;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int chunk = ((4 * (cq & 1) + e) ^ (row & 7)) * 16;
+                *reinterpret_cast<float4 *>(base + chunk) =
+                    make_float4(__uint_as_float(r[4 * e]) * f, __uint_as_float(r[4 * e + 1]) * f,
+                                __uint_as_float(r[4 * e + 2]) * f, __uint_as_float(r[4 * e + 3]) * f);
+            }
+        };
+        // dQ of iteration n (its barrier phase has been waited for): scale this thread's 16 columns
+        // into the staging tile; warp 3 adds the tile into dqkv with one bulk reduction per half.
+        auto flush_dq = [&](int n) -> bool {
+            if (n >= 1 && !mbar_wait_warp(&sm.out_free, (n - 1) & 1, ctx, SITE_OUT_FREE)) return false;
             tc_fence_after_sync();
-            const int t = (jt + n) * kTile + row;
             uint32_t r[16];
             tmem_ld16(tmem + lane_addr + kColDQ + (n & 1) * kD + 16 * cq, r);
             tmem_wait_ld();
-#ifdef ATTN_EXPERIMENT_NO_DQ
-            if (false) {
-#else
-            if (t < T) {
-#endif
-                float4 *dst = reinterpret_cast<float4 *>(dqkv + ((size_t)b * T + t) * C3 + (size_t)h * kD + 16 * cq);
-#pragma unroll
-                for (int e = 0; e < 4; e++)  // fire-and-forget vector reduction: nothing is returned
-                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e),
-                                 "f"(__uint_as_float(r[4 * e]) * scale), "f"(__uint_as_float(r[4 * e + 1]) * scale),
-                                 "f"(__uint_as_float(r[4 * e + 2]) * scale), "f"(__uint_as_float(r[4 * e + 3]) * scale)
-                                 : "memory");
-            }
+            stage_row(sm.dqs[0], r, scale);
+            fence_proxy_async_smem();
+            mbar_arrive(&sm.out_full);
+            return true;
         };
 
         BWD_LIFE(1);
@@ -421,7 +434,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     ok = false;
                     break;
                 }
-                flush_dq(n - 1);
+                if (!flush_dq(n - 1)) { ok = false; break; }
             }
             BWD_TRACE(threadIdx.x == 128, 1, n, 7);
             // half B: queries 64..127
@@ -447,30 +460,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
         BWD_LIFE(2);
         BWD_EPI(0);
-        if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {
-            BWD_EPI(1);
-            flush_dq(niter - 1);
+        if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST) &&
+            flush_dq(niter - 1)) {
             BWD_EPI(2);
-            // the last dQ commit also covers every dV / dK MMA
-            const int t = jt * kTile + row;
+            // The last dQ commit also covers every dV / dK MMA, so K and V in shared memory are dead:
+            // their space stages the dK and dV tiles for the copy engine.
             uint32_t rk[16], rv[16];
             tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
             tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
             tmem_wait_ld();
             BWD_EPI(3);
-            if (t < T) {
-                float *dk_dst = dqkv + ((size_t)b * T + t) * C3 + C + (size_t)h * kD + 16 * cq;
-                float *dv_dst = dk_dst + C;
-#pragma unroll
-                for (int e = 0; e < 16; e += 4) {
-                    *reinterpret_cast<float4 *>(dk_dst + e) =
-                        make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
-                                    __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
-                    *reinterpret_cast<float4 *>(dv_dst + e) =
-                        make_float4(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1]), __uint_as_float(rv[e + 2]),
-                                    __uint_as_float(rv[e + 3]));
-                }
+            stage_row(sm.k[0], rk, scale);
+            stage_row(sm.v[0], rv, 1.f);
+            fence_proxy_async_smem();
+            mbar_arrive(&sm.out_full);
+        }
+    } else if (warp == 3) {
+        // ------------------------------ output copies ------------------------------
+        // dQ tiles are added into dqkv (several key tiles contribute to one query tile), dK and dV
+        // are plain stores.  Rows past the end of the sequence are dropped by the copy engine.
+        if (lane == 0) {
+            tma_prefetch_desc(&map_dx);
+            const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
+            bool ok = true;
+            for (int n = 0; ok && n < niter; n++) {
+                ok = mbar_wait(&sm.out_full, n & 1, ctx, SITE_OUT_FULL);
+                if (!ok) break;
+                tma_reduce_add_3d(sm.dqs[0], &map_dx, xq, (jt + n) * kTile, b);
+                tma_reduce_add_3d(sm.dqs[1], &map_dx, xq + 32, (jt + n) * kTile, b);
+                bulk_commit();
+                bulk_wait_read_all();
+                mbar_arrive(&sm.out_free);
             }
+            if (ok && mbar_wait(&sm.out_full, niter & 1, ctx, SITE_OUT_FULL)) {
+                tma_store_3d(sm.k[0], &map_dx, xk, jt * kTile, b);
+                tma_store_3d(sm.k[1], &map_dx, xk + 32, jt * kTile, b);
+                tma_store_3d(sm.v[0], &map_dx, xv, jt * kTile, b);
+                tma_store_3d(sm.v[1], &map_dx, xv + 32, jt * kTile, b);
+                bulk_commit();
+            }
+            bulk_wait_all();  // shared memory must stay alive until the copies have read it
         }
     }
 
@@ -501,19 +530,21 @@ extern "C" int attn_bwd_life_read(long long *dst) {
 }
 #endif
 
-static size_t bwd_smem_bytes() { return sizeof(BwdSmem) + 1024; }
+static size_t bwd_smem_bytes() { return sizeof(BwdSmem); }
+static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward kernel shared memory");
 
 cudaError_t fast_bwd_set_attributes() {
     return cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem_bytes());
 }
 
-// map_x / map_do must have boxes of 64 rows (see the producer warp).
-cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const float *lse,
+// map_x / map_do must have boxes of 64 rows (see the producer warp); map_dx covers dqkv as fp32
+// {3C, T, B} with boxes of 32 columns x 128 rows, 128-byte swizzle.
+cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
                                  const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s) {
     const int nt = (T + kTile - 1) / kTile;
     const unsigned grid = (unsigned)(nt * B * H);
     const float scale = 0.125f;  // 1/sqrt(64)
-    attn_bwd_kernel<<<grid, kThreads, bwd_smem_bytes(), s>>>(map_x, map_do, lse, delta, dqkv, B, T, H, scale,
+    attn_bwd_kernel<<<grid, kThreads, bwd_smem_bytes(), s>>>(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, scale,
                                                              scale * 1.4426950408889634f, status);
     return cudaGetLastError();
 }
