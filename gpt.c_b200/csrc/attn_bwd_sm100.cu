@@ -29,8 +29,10 @@
 // group (0..3) selects 16 of the 64 query columns of a half and 16 of the 64 columns of
 // dQ / dK / dV.
 //
-// Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ0 [384,448)
-// dQ1 [448,512).  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes
+// Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448)
+// K hi [448,480)  V hi [480,512).  The hi planes of K and V are copied there once so that two of
+// the three terms of S^T and dP^T take their A operand from tensor memory: shared-memory
+// bandwidth, not the tensor pipe, is what limits this kernel.  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes
 // 8 columns of packed bf16 hi parts followed by 8 columns of packed lo parts.
 #include "attn_internal.h"
 #include "tc05.cuh"
@@ -45,33 +47,37 @@ constexpr int kHalf = 64;
 constexpr int kD = 64;
 constexpr int kPlaneTile = kTile * kD * 2;  // 16 KiB: one bf16 plane of a 128-row tile
 constexpr int kPlaneHalf = kHalf * kD * 2;  // 8 KiB
+constexpr int kSlots = 3;                   // Q/dO half tiles in flight
 constexpr int kThreads = 640;
+constexpr int kGradWarp = 3;
 constexpr int kComputeThreads = 512;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ = 384, kColKH = 448, kColVH = 480;
 
 struct __align__(1024) BwdSmem {
     uint8_t k[2][kPlaneTile];      // K_j   [plane]
     uint8_t v[2][kPlaneTile];      // V_j
-    uint8_t q[2][kPlaneTile];      // Q_i   (rows 0-63 = half A, 64-127 = half B)
-    uint8_t g[2][kPlaneTile];      // dO_i
-    uint8_t ds[2][2][kPlaneTile];  // dS^T  [plane][query half][128 keys x 64 queries]
-    uint8_t dqs[2][kPlaneTile];    // fp32 dQ tile on its way out: [32-column half][128 queries x 128 bytes]
+    uint8_t in[kSlots][4][kPlaneHalf];  // ring of query half tiles: [slot][Q hi, Q lo, dO hi, dO lo][64 rows]
+    // dS^T [plane][query half][128 keys x 64 queries].  Between two dQ products the first 32 KiB
+    // also stage the finished fp32 dQ tile on its way out: [32-column half][128 queries x 128 bytes].
+    uint8_t ds[2][2][kPlaneTile];
     float lse2[2][kTile];          // -log-sum-exp of the query tile in log2 units, double buffered
     float delta[2][kTile];         // -rowsum(dO * O)
     uint64_t kv_full;
-    uint64_t q_full[2], q_empty[2], g_full[2], g_empty[2];  // [half]
+    uint64_t in_full[kSlots], in_empty[kSlots];
     uint64_t st_full[2], pds_full[2];                       // [half]
+    uint64_t ds_full;                                       // dS^T of both halves is in shared memory
     uint64_t dq_full[2];                                    // [iteration parity]
-    uint64_t out_full, out_free;                            // staged output tile: written / read by the copy engine
-    uint64_t row_bar;
+    uint64_t out_full, out_free;                            // staged dQ tile: written / read by the copy engine
+    uint64_t kv_out_full;                                   // staged dK / dV tiles written
+    uint64_t stats_full[2], stats_free[2], kv_tmem;  // [statistics buffer]
     uint32_t tmem_base;
     int abort_flag;
 };
 
 enum Site : int {
-    SITE_Q_EMPTY = 101, SITE_G_EMPTY, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
-    SITE_MMA_IDLE, SITE_OUT_FULL, SITE_OUT_FREE, SITE_SMEM_ALIGN
+    SITE_IN_EMPTY = 101, SITE_IN_FULL, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
+    SITE_MMA_IDLE, SITE_STATS_FREE, SITE_KV_TMEM, SITE_OUT_FULL, SITE_OUT_FREE, SITE_SMEM_ALIGN
 };
 
 // Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
@@ -180,17 +186,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         sm.abort_flag = 0;
         mbar_init(&sm.kv_full, 1);
         for (int i = 0; i < 2; i++) {
-            mbar_init(&sm.q_full[i], 1);
-            mbar_init(&sm.q_empty[i], 1);
-            mbar_init(&sm.g_full[i], 1);
-            mbar_init(&sm.g_empty[i], 1);
             mbar_init(&sm.st_full[i], 1);
             mbar_init(&sm.pds_full[i], kComputeThreads);
             mbar_init(&sm.dq_full[i], 1);
         }
-        mbar_init(&sm.row_bar, 128);
+        for (int i = 0; i < kSlots; i++) {
+            mbar_init(&sm.in_full[i], 1);
+            mbar_init(&sm.in_empty[i], 1);
+        }
+        mbar_init(&sm.ds_full, kComputeThreads);
+        mbar_init(&sm.stats_full[0], 32);
+        mbar_init(&sm.stats_full[1], 32);
+        mbar_init(&sm.stats_free[0], kComputeThreads / 32);
+        mbar_init(&sm.stats_free[1], kComputeThreads / 32);
+        mbar_init(&sm.kv_tmem, kComputeThreads);
         mbar_init(&sm.out_full, kComputeThreads);
         mbar_init(&sm.out_free, 1);
+        mbar_init(&sm.kv_out_full, kComputeThreads);
         fence_barrier_init();
     }
     if (warp == 2) {
@@ -215,130 +227,133 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     tma_load_4d(sm.v[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xv, jt * kTile + hf * kHalf, b, pl);
                 }
             }
-            bool ok = true;
-            for (int n = 0; ok && n < niter; n++) {
-                // the halves are released in the order dO_A, Q_A, dO_B, Q_B
-                for (int hf = 0; ok && hf < 2; hf++) {
-                    const int y = (jt + n) * kTile + hf * kHalf;
-                    if (n >= 1 && !mbar_wait(&sm.g_empty[hf], (n - 1) & 1, ctx, SITE_G_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(&sm.g_full[hf], 2 * kPlaneHalf);
-                    tma_load_4d(sm.g[0] + hf * kPlaneHalf, &map_do, &sm.g_full[hf], h * kD, y, b, 0);
-                    tma_load_4d(sm.g[1] + hf * kPlaneHalf, &map_do, &sm.g_full[hf], h * kD, y, b, 1);
-                    if (n >= 1 && !mbar_wait(&sm.q_empty[hf], (n - 1) & 1, ctx, SITE_Q_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(&sm.q_full[hf], 2 * kPlaneHalf);
-                    tma_load_4d(sm.q[0] + hf * kPlaneHalf, &map_x, &sm.q_full[hf], xq, y, b, 0);
-                    tma_load_4d(sm.q[1] + hf * kPlaneHalf, &map_x, &sm.q_full[hf], xq, y, b, 1);
-                }
+            // Half tile t = 2n + half goes to slot t % 3; a slot is free again once the dV / dK
+            // products that read it have completed.
+            for (int t = 0, slot = 0, use = 0; t < 2 * niter; t++) {
+                if (use >= 1 && !mbar_wait(&sm.in_empty[slot], (use - 1) & 1, ctx, SITE_IN_EMPTY)) break;
+                const int y = (jt + (t >> 1)) * kTile + (t & 1) * kHalf;
+                mbar_expect_tx(&sm.in_full[slot], 4 * kPlaneHalf);
+                tma_load_4d(sm.in[slot][0], &map_x, &sm.in_full[slot], xq, y, b, 0);
+                tma_load_4d(sm.in[slot][1], &map_x, &sm.in_full[slot], xq, y, b, 1);
+                tma_load_4d(sm.in[slot][2], &map_do, &sm.in_full[slot], h * kD, y, b, 0);
+                tma_load_4d(sm.in[slot][3], &map_do, &sm.in_full[slot], h * kD, y, b, 1);
+                if (++slot == kSlots) { slot = 0; use++; }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+        // ------------------------------ MMA issuer: S^T, dP^T ------------------------------
         constexpr uint32_t idesc_st = idesc_bf16_f32(kTile, kHalf, 0, 0);  // S^T, dP^T of one half (N = 64)
-        constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);     // dV, dK (A in TMEM)
-        constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);     // dQ (A, B MN-major)
         // K-major views (rows of 64 head-dim values)
         const uint64_t k_km[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
         const uint64_t v_km[2] = {smem_desc_sw128(smem_u32(sm.v[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.v[1]), 16, 1024)};
-        const uint64_t q_km[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
-        const uint64_t g_km[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.g[1]), 16, 1024)};
-        // MN-major views of the same bytes (the row index is the contraction index)
-        const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
-        const uint64_t q_mn[2] = {smem_desc_sw128(smem_u32(sm.q[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.q[1]), 1024, 1024)};
-        const uint64_t g_mn[2] = {smem_desc_sw128(smem_u32(sm.g[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.g[1]), 1024, 1024)};
-        const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
-                                   smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
+        // Q/dO ring: descriptors of slot 0, plane 0; slot s, plane p lies (4 s + p) * 8 KiB further
+        const uint64_t in_km = smem_desc_sw128(smem_u32(sm.in[0][0]), 16, 1024);
 
-        bool ok = mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL);
-        // Two task streams, each in order: score tasks s = 2n + half (S^T, dP^T of one half) and
-        // gradient tasks g = 2n + half (dV, dK of one half; half B also issues dQ).  A score task may
-        // run once its Q/dO half has landed and the gradient task that read the columns it
-        // overwrites (g = s - 2) has been issued.  Score tasks have priority.
-        const int ntask = 2 * niter;
-        int s_idx = 0, g_idx = 0;
+        // Score tasks t = 2n + half, in order: S^T and dP^T of one half of a query tile.  Task t
+        // overwrites the columns task t-2 produced, so the dV / dK products that consumed those
+        // (gradient task t-2, issued by another warp) must have completed.
+        bool ok = mbar_wait_warp(&sm.kv_tmem, 0, ctx, SITE_KV_TMEM);
+        tc_fence_after_sync();
+        const uint32_t leader = elect_leader();  // the one lane that issues every MMA and commit of this warp
+        int s_slot = 0, s_use = 0, e_slot = 0, e_use = 0;
+        for (int t = 0; ok && t < 2 * niter; t++) {
+            const int n = t >> 1, hf = t & 1;
+            if (t >= 2) {
+                ok = mbar_wait_warp(&sm.in_empty[e_slot], e_use & 1, ctx, SITE_IN_EMPTY);
+                if (++e_slot == kSlots) { e_slot = 0; e_use++; }
+            }
+            ok = ok && mbar_wait_warp(&sm.in_full[s_slot], s_use & 1, ctx, SITE_IN_FULL);
+            if (!ok) break;
+            const uint64_t q_km = desc_advance(in_km, s_slot * 4 * kPlaneHalf);
+            const uint64_t g_km = desc_advance(q_km, 2 * kPlaneHalf);
+            tc_fence_after_sync();
+            BWD_TRACE(lane == 0, 0, n, 0 + 4 * hf);
+            uint32_t acc = 0;
+#pragma unroll
+            for (int term = 0; term < 3; term++) {
+                const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; kk++) {
+                    if (term < 2)
+                        mma_ts_lead(leader, tmem + kColST + hf * kHalf, tmem + kColKH + 8 * kk,
+                                     desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                    else
+                        mma_ss_lead(leader, tmem + kColST + hf * kHalf, desc_advance(k_km[a], kk * 32),
+                                     desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                    acc = 1;
+                }
+            }
+            acc = 0;
+#pragma unroll
+            for (int term = 0; term < 3; term++) {
+                const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; kk++) {
+                    if (term < 2)
+                        mma_ts_lead(leader, tmem + kColDPT + hf * kHalf, tmem + kColVH + 8 * kk,
+                                     desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                    else
+                        mma_ss_lead(leader, tmem + kColDPT + hf * kHalf, desc_advance(v_km[a], kk * 32),
+                                     desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                    acc = 1;
+                }
+            }
+            tc_commit_lead(leader, &sm.st_full[hf]);
+            BWD_TRACE(lane == 0, 0, n, 1 + 4 * hf);
+            if (++s_slot == kSlots) { s_slot = 0; s_use++; }
+        }
+    } else if (warp == 2) {
+        // ------------------------------ row statistics and output copies ------------------------------
+        // Two small jobs polled by one warp.  (1) -lse * log2(e) and -delta of every query tile,
+        // double buffered in shared memory; each buffer has its own full / free barriers, so this
+        // warp can never be two phases ahead of a reader of the same barrier.  (2) Staged dQ tiles
+        // are added into dqkv (several key tiles contribute to one query tile), the final dK / dV
+        // tiles are plain stores; rows past the end of the sequence are dropped by the copy engine.
+        if (lane == 0) tma_prefetch_desc(&map_dx);
+        const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
+        int m = 0, o = 0;
+        bool kv_stored = false, ok = true;
         uint64_t idle_since = 0;
         uint32_t idle_polls = 0;
-        while (ok && g_idx < ntask) {
+        while (ok && !kv_stored) {
             bool progressed = false;
-            if (s_idx < ntask && g_idx >= s_idx - 1) {
-                const int n = s_idx >> 1, hf = s_idx & 1;
-                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.q_full[hf], n & 1) && mbar_test_wait(&sm.g_full[hf], n & 1))) {
-                    tc_fence_after_sync();
-                    BWD_TRACE(lane == 0, 0, n, 0 + 4 * hf);
-                    uint32_t acc = 0;
+            if (m < niter) {
+                const int buf = m & 1;
+                if (m < 2 || __all_sync(0xffffffffu, mbar_test_wait(&sm.stats_free[buf], ((m >> 1) - 1) & 1))) {
 #pragma unroll
-                    for (int term = 0; term < 3; term++) {
-                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                        for (int kk = 0; kk < kD / 16; kk++) {
-                            mma_ss_elect(tmem + kColST + hf * kHalf, desc_advance(k_km[a], kk * 32),
-                                         desc_advance(q_km[bb], hf * kPlaneHalf + kk * 32), idesc_st, acc);
-                            acc = 1;
-                        }
+                    for (int k = 0; k < kTile / 32; k++) {
+                        const int r = lane + 32 * k, t = (jt + m) * kTile + r;
+                        sm.lse2[buf][r] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
+                        sm.delta[buf][r] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
                     }
-                    acc = 0;
-#pragma unroll
-                    for (int term = 0; term < 3; term++) {
-                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                        for (int kk = 0; kk < kD / 16; kk++) {
-                            mma_ss_elect(tmem + kColDPT + hf * kHalf, desc_advance(v_km[a], kk * 32),
-                                         desc_advance(g_km[bb], hf * kPlaneHalf + kk * 32), idesc_st, acc);
-                            acc = 1;
-                        }
-                    }
-                    tc_commit_elect(&sm.st_full[hf]);
-                    BWD_TRACE(lane == 0, 0, n, 1 + 4 * hf);
-                    s_idx++;
+                    mbar_arrive(&sm.stats_full[buf]);
+                    m++;
                     progressed = true;
                 }
             }
-            if (g_idx < s_idx) {
-                const int n = g_idx >> 1, hf = g_idx & 1;
-                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.pds_full[hf], n & 1))) {
-                    tc_fence_after_sync();
-                    BWD_TRACE(lane == 0, 0, n, 2 + 4 * hf);
-                    // dV += P^T dO_i over this half's 64 queries (4 K-steps of 16)
-#pragma unroll
-                    for (int term = 0; term < 3; term++) {
-                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                        for (int k4 = 0; k4 < 4; k4++) {
-                            const int kk = 4 * hf + k4;
-                            mma_ts_elect(tmem + kColDV, tmem + kColST + 16 * kk + 8 * a, desc_advance(g_mn[bb], kk * 2048),
-                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
-                        }
+            if (o < niter) {
+                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.out_full, o & 1))) {
+                    if (lane == 0) {
+                        tma_reduce_add_3d(sm.ds[0][0], &map_dx, xq, (jt + o) * kTile, b);
+                        tma_reduce_add_3d(sm.ds[0][1], &map_dx, xq + 32, (jt + o) * kTile, b);
+                        bulk_commit();
+                        bulk_wait_read_all();
+                        mbar_arrive(&sm.out_free);
                     }
-                    tc_commit_elect(&sm.g_empty[hf]);
-                    // dK += dS^T Q_i
-#pragma unroll
-                    for (int term = 0; term < 3; term++) {
-                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                        for (int k4 = 0; k4 < 4; k4++) {
-                            const int kk = 4 * hf + k4;
-                            mma_ts_elect(tmem + kColDK, tmem + kColDPT + 16 * kk + 8 * a, desc_advance(q_mn[bb], kk * 2048),
-                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
-                        }
-                    }
-                    tc_commit_elect(&sm.q_empty[hf]);
-                    if (hf == 1) {
-                        // dQ_i = dS K_j over all 128 keys; both halves of dS^T are in shared memory now
-                        const uint32_t d_q = tmem + kColDQ + (n & 1) * kD;
-#pragma unroll
-                        for (int term = 0; term < 3; term++) {
-                            const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                            for (int kk = 0; kk < kTile / 16; kk++) {
-                                mma_ss_elect(d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048),
-                                             idesc_dq, (term > 0 || kk > 0) ? 1u : 0u);
-                            }
-                        }
-                        tc_commit_elect(&sm.dq_full[n & 1]);
-                    }
-                    BWD_TRACE(lane == 0, 0, n, 3 + 4 * hf);
-                    g_idx++;
+                    __syncwarp();
+                    o++;
                     progressed = true;
                 }
+            } else if (__all_sync(0xffffffffu, mbar_test_wait(&sm.kv_out_full, 0))) {
+                if (lane == 0) {
+                    tma_store_3d(sm.k[0], &map_dx, xk, jt * kTile, b);
+                    tma_store_3d(sm.k[1], &map_dx, xk + 32, jt * kTile, b);
+                    tma_store_3d(sm.v[0], &map_dx, xv, jt * kTile, b);
+                    tma_store_3d(sm.v[1], &map_dx, xv + 32, jt * kTile, b);
+                    bulk_commit();
+                }
+                kv_stored = true;
+                progressed = true;
             }
             if (progressed) {
                 idle_polls = 0;
@@ -349,12 +364,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (__any_sync(0xffffffffu, give_up)) {
                     if (lane == 0 && !sm.abort_flag) {
                         sm.abort_flag = 1;
-                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_MMA_IDLE);
+                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_OUT_FULL);
                     }
                     ok = false;
                 }
             }
         }
+        if (lane == 0) bulk_wait_all();  // shared memory must stay alive until the copies have read it
+        __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------ compute group ------------------------------
         const int quarter = warp & 3;
@@ -380,41 +397,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // dQ of iteration n (its barrier phase has been waited for): scale this thread's 16 columns
         // into the staging tile; warp 3 adds the tile into dqkv with one bulk reduction per half.
         auto flush_dq = [&](int n) -> bool {
-            if (n >= 1 && !mbar_wait_warp(&sm.out_free, (n - 1) & 1, ctx, SITE_OUT_FREE)) return false;
             tc_fence_after_sync();
             uint32_t r[16];
-            tmem_ld16(tmem + lane_addr + kColDQ + (n & 1) * kD + 16 * cq, r);
+            tmem_ld16(tmem + lane_addr + kColDQ + 16 * cq, r);
             tmem_wait_ld();
-            stage_row(sm.dqs[0], r, scale);
+            stage_row(sm.ds[0][0], r, scale);
             fence_proxy_async_smem();
             mbar_arrive(&sm.out_full);
             return true;
         };
 
+        // K hi and V hi, this thread's 16 head-dim values of key `row`, into tensor memory (packed
+        // pairs, so 8 columns each); the rows in shared memory are 128-byte swizzled.
+        if (!mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL)) ok = false;
+        if (ok) {
+            uint32_t kh[8], vh[8];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int off = row * 128 + (((2 * cq + j) ^ (row & 7)) << 4);
+                const uint4 a = *reinterpret_cast<const uint4 *>(sm.k[0] + off);
+                const uint4 c = *reinterpret_cast<const uint4 *>(sm.v[0] + off);
+                kh[4 * j] = a.x, kh[4 * j + 1] = a.y, kh[4 * j + 2] = a.z, kh[4 * j + 3] = a.w;
+                vh[4 * j] = c.x, vh[4 * j + 1] = c.y, vh[4 * j + 2] = c.z, vh[4 * j + 3] = c.w;
+            }
+            tmem_st8(tmem + lane_addr + kColKH + 8 * cq, kh);
+            tmem_st8(tmem + lane_addr + kColVH + 8 * cq, vh);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.kv_tmem);
+        }
         BWD_LIFE(1);
         const float2 sc2 = make_float2(scale_log2, scale_log2);
-        if (cq == 0) {  // statistics of the first query tile
-            const int t = jt * kTile + row;
-            sm.lse2[0][row] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
-            sm.delta[0][row] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
-            mbar_arrive(&sm.row_bar);
-        }
-        for (int n = 0; n < niter; n++) {
+        for (int n = 0; ok && n < niter; n++) {
             const int it = jt + n;
             const bool diag = (n == 0);
             const int lb = n & 1;
-            // Column group 0 stages the row statistics of every query tile for everybody, one tile
-            // ahead: the values of tile n+1 are fetched now and published after the wait on half B
-            // of this tile (by then nobody reads that buffer any more).
-            float next_lse = 0.f, next_delta = 0.f;  // raw loads; the arithmetic waits until they are published
-            if (cq == 0 && n + 1 < niter) {
-                const int t = (it + 1) * kTile + row;
-                if (t < T) {
-                    next_lse = lse[(size_t)bh * T + t];
-                    next_delta = delta[(size_t)bh * T + t];
-                }
-            }
-            if (!mbar_wait_warp(&sm.row_bar, n & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
+            // row statistics of this query tile (warp 2 stages them up to two tiles ahead)
+            if (!mbar_wait_warp(&sm.stats_full[lb], (n >> 1) & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
 
             uint32_t dh_a[8], dl_a[8], dh_b[8], dl_b[8];
             // half A: queries 0..63 of the tile
@@ -427,8 +446,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_before_sync();
             mbar_arrive(&sm.pds_full[0]);  // dV / dK of half A may start; dS^T goes to shared memory below
             BWD_TRACE(threadIdx.x == 128, 1, n, 2);
-            // While the tensor cores work on half B's scores: the previous tile's dQ has finished by
-            // now, add it into the output.  That also frees the dS^T tile in shared memory.
+            // While the tensor cores work on half B's scores: the previous tile's dQ (issued as soon as
+            // its dS^T was stored) has finished by now; move it out.  The copy engine reads the staged
+            // tile while half B is computed, then dS^T of this tile may overwrite it.
             if (n >= 1) {
                 if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
                     ok = false;
@@ -440,21 +460,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // half B: queries 64..127
             if (!mbar_wait_warp(&sm.st_full[1], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
             tc_fence_after_sync();
-            if (cq == 0 && n + 1 < niter) {  // S^T of half B exists, so every thread is done with tile n-1
-                sm.lse2[lb ^ 1][row] = -next_lse * 1.4426950408889634f;
-                sm.delta[lb ^ 1][row] = -next_delta;
-                mbar_arrive(&sm.row_bar);
-            }
             BWD_TRACE(threadIdx.x == 128, 1, n, 3);
             compute_run(sm, t_st + kHalf, t_dpt + kHalf, lb, kHalf + 16 * cq, row, diag, sc2, dh_b, dl_b);
             BWD_TRACE(threadIdx.x == 128, 1, n, 4);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.pds_full[1]);  // dV / dK of half B may start
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.stats_free[lb]);  // this warp has read the tile's statistics
             BWD_TRACE(threadIdx.x == 128, 1, n, 5);
+            // the staged dQ tile of the previous iteration must have left shared memory
+            if (n >= 1 && !mbar_wait_warp(&sm.out_free, (n - 1) & 1, ctx, SITE_OUT_FREE)) { ok = false; break; }
             store_ds(sm.ds[0][0], sm.ds[1][0], row, cq, dh_a, dl_a);
             store_ds(sm.ds[0][1], sm.ds[1][1], row, cq, dh_b, dl_b);
-            tmem_wait_st();
             fence_proxy_async_smem();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.pds_full[1]);
+            mbar_arrive(&sm.ds_full);  // dQ may start
             BWD_TRACE(threadIdx.x == 128, 1, n, 6);
         }
 
@@ -473,33 +493,101 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             stage_row(sm.k[0], rk, scale);
             stage_row(sm.v[0], rv, 1.f);
             fence_proxy_async_smem();
-            mbar_arrive(&sm.out_full);
+            mbar_arrive(&sm.kv_out_full);
         }
-    } else if (warp == 3) {
-        // ------------------------------ output copies ------------------------------
-        // dQ tiles are added into dqkv (several key tiles contribute to one query tile), dK and dV
-        // are plain stores.  Rows past the end of the sequence are dropped by the copy engine.
-        if (lane == 0) {
-            tma_prefetch_desc(&map_dx);
-            const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
-            bool ok = true;
-            for (int n = 0; ok && n < niter; n++) {
-                ok = mbar_wait(&sm.out_full, n & 1, ctx, SITE_OUT_FULL);
-                if (!ok) break;
-                tma_reduce_add_3d(sm.dqs[0], &map_dx, xq, (jt + n) * kTile, b);
-                tma_reduce_add_3d(sm.dqs[1], &map_dx, xq + 32, (jt + n) * kTile, b);
-                bulk_commit();
-                bulk_wait_read_all();
-                mbar_arrive(&sm.out_free);
+    } else if (warp == kGradWarp) {
+        // ------------------------------ MMA issuer: dV, dK, dQ ------------------------------
+        // Two task streams, each in order: gradient tasks g = 2n + half (dV, dK of one half, once the
+        // compute warps have turned that half into P^T / dS^T) and one dQ task per query tile (once
+        // dS^T is in shared memory).  Whichever is ready goes first, dQ before dV / dK: the compute
+        // warps need its result, and its operand buffer, one tile later.
+        constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);  // dV, dK (A in TMEM)
+        constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);  // dQ (A, B MN-major)
+        // MN-major views: the row index is the contraction index
+        const uint64_t in_mn = smem_desc_sw128(smem_u32(sm.in[0][0]), 1024, 1024);
+        const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
+        const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
+                                   smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
+        const int ntask = 2 * niter;
+        int g_idx = 0, d_idx = 0, g_slot = 0;
+        const uint32_t leader = elect_leader();
+        bool ok = true;
+        uint64_t idle_since = 0;
+        uint32_t idle_polls = 0;
+        while (ok && d_idx < niter) {
+            bool progressed = false;
+            if (2 * d_idx + 1 < g_idx) {
+                // dQ_i = dS K_j over all 128 keys
+                const int n = d_idx;
+                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.ds_full, n & 1))) {
+                    tc_fence_after_sync();
+                    BWD_TRACE(lane == 0, 1, 8 + (n & 7), 0);
+                    const uint32_t d_q = tmem + kColDQ;
+#pragma unroll
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                        for (int kk = 0; kk < kTile / 16; kk++) {
+                            mma_ss_lead(leader, d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048),
+                                        idesc_dq, (term > 0 || kk > 0) ? 1u : 0u);
+                        }
+                    }
+                    tc_commit_lead(leader, &sm.dq_full[n & 1]);
+                    BWD_TRACE(lane == 0, 1, 8 + (n & 7), 1);
+                    d_idx++;
+                    progressed = true;
+                }
             }
-            if (ok && mbar_wait(&sm.out_full, niter & 1, ctx, SITE_OUT_FULL)) {
-                tma_store_3d(sm.k[0], &map_dx, xk, jt * kTile, b);
-                tma_store_3d(sm.k[1], &map_dx, xk + 32, jt * kTile, b);
-                tma_store_3d(sm.v[0], &map_dx, xv, jt * kTile, b);
-                tma_store_3d(sm.v[1], &map_dx, xv + 32, jt * kTile, b);
-                bulk_commit();
+            if (g_idx < ntask) {
+                const int n = g_idx >> 1, hf = g_idx & 1;
+                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.pds_full[hf], n & 1))) {
+                    tc_fence_after_sync();
+                    const uint64_t q_mn = desc_advance(in_mn, g_slot * 4 * kPlaneHalf);
+                    const uint64_t g_mn = desc_advance(q_mn, 2 * kPlaneHalf);
+                    BWD_TRACE(lane == 0, 0, n, 2 + 4 * hf);
+                    // dV += P^T dO_i over this half's 64 queries (4 K-steps of 16)
+#pragma unroll
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            const int kk = 4 * hf + k4;
+                            mma_ts_lead(leader, tmem + kColDV, tmem + kColST + 16 * kk + 8 * a, desc_advance(g_mn, bb * kPlaneHalf + k4 * 2048),
+                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                        }
+                    }
+                    // dK += dS^T Q_i
+#pragma unroll
+                    for (int term = 0; term < 3; term++) {
+                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            const int kk = 4 * hf + k4;
+                            mma_ts_lead(leader, tmem + kColDK, tmem + kColDPT + 16 * kk + 8 * a, desc_advance(q_mn, bb * kPlaneHalf + k4 * 2048),
+                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                        }
+                    }
+                    tc_commit_lead(leader, &sm.in_empty[g_slot]);
+                    if (++g_slot == kSlots) g_slot = 0;
+                    BWD_TRACE(lane == 0, 0, n, 3 + 4 * hf);
+                    g_idx++;
+                    progressed = true;
+                }
             }
-            bulk_wait_all();  // shared memory must stay alive until the copies have read it
+            if (progressed) {
+                idle_polls = 0;
+            } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up when nothing became ready for a second
+                const uint64_t now = global_timer_ns();
+                if (idle_polls == 256u) idle_since = now;
+                const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
+                if (__any_sync(0xffffffffu, give_up)) {
+                    if (lane == 0 && !sm.abort_flag) {
+                        sm.abort_flag = 1;
+                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_MMA_IDLE);
+                    }
+                    ok = false;
+                }
+            }
         }
     }
 

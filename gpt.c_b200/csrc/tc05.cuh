@@ -286,6 +286,57 @@ __device__ __forceinline__ void tc_commit_elect(uint64_t *bar) {
         : "memory");
 }
 
+// The same with the election done once by the caller (elect_leader) for a whole batch of
+// instructions: every MMA of a batch and the commit that tracks them are issued by one thread.
+__device__ __forceinline__ uint32_t elect_leader() {
+    uint32_t is_leader;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, e;\n\t"
+        "}"
+        : "=r"(is_leader));
+    return is_leader;
+}
+
+__device__ __forceinline__ void mma_ss_lead(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_ts_lead(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_lead(uint32_t leader, uint64_t *bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "setp.ne.b32 e, %1, 0;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}"
+        ::"r"(smem_u32(bar)), "r"(leader)
+        : "memory");
+}
+
 // ------------------------------------------------------------------------------------------
 // Tensor-memory loads / stores, shape 32x32b: lane t of the warp accesses TMEM lane
 // (lane_base + t) and N consecutive 32-bit columns.  A warp may only touch the 32 lanes
