@@ -91,6 +91,7 @@ __device__ long long g_bwd_trace[2 * 16 * 8];
 __device__ long long g_bwd_life[16 * 4];
 __device__ long long g_bwd_epi[8];
 #define BWD_EPI(k) do { if (blockIdx.x == 0 && threadIdx.x == 128) g_bwd_epi[k] = (long long)global_timer_ns(); } while (0)
+#define BWD_EPI2(k) do { if (blockIdx.x == 0) g_bwd_epi[k] = (long long)global_timer_ns(); } while (0)
 #define BWD_LIFE(k)                                                                          \
     do {                                                                                     \
         if (threadIdx.x == 128 && blockIdx.x % 48 == 0)                                      \
@@ -98,6 +99,7 @@ __device__ long long g_bwd_epi[8];
     } while (0)
 #else
 #define BWD_EPI(k) do {} while (0)
+#define BWD_EPI2(k) do {} while (0)
 #define BWD_LIFE(k) \
     do {            \
     } while (0)
@@ -204,6 +206,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         mbar_init(&sm.out_free, 1);
         mbar_init(&sm.kv_out_full, kComputeThreads);
         fence_barrier_init();
+        // This thread is also the TMA producer: K, V and the first Q/dO half tiles are requested
+        // right away, while the other warps are still setting up.
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_do);
+        const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
+        mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
+        for (int hf = 0; hf < 2; hf++) {
+            for (int pl = 0; pl < 2; pl++) {
+                tma_load_4d(sm.k[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xk, jt * kTile + hf * kHalf, b, pl);
+                tma_load_4d(sm.v[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xv, jt * kTile + hf * kHalf, b, pl);
+            }
+        }
+        for (int t = 0; t < kSlots && t < 2 * niter; t++) {
+            const int y = (jt + (t >> 1)) * kTile + (t & 1) * kHalf;
+            mbar_expect_tx(&sm.in_full[t], 4 * kPlaneHalf);
+            tma_load_4d(sm.in[t][0], &map_x, &sm.in_full[t], xq, y, b, 0);
+            tma_load_4d(sm.in[t][1], &map_x, &sm.in_full[t], xq, y, b, 1);
+            tma_load_4d(sm.in[t][2], &map_do, &sm.in_full[t], h * kD, y, b, 0);
+            tma_load_4d(sm.in[t][3], &map_do, &sm.in_full[t], h * kD, y, b, 1);
+        }
     }
     if (warp == 2) {
         tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -217,20 +240,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (warp == 0) {
         // ------------------------------ TMA producer (boxes of 64 rows) ------------------------------
         if (lane == 0) {
-            tma_prefetch_desc(&map_x);
-            tma_prefetch_desc(&map_do);
-            const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
-            mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
-            for (int hf = 0; hf < 2; hf++) {
-                for (int pl = 0; pl < 2; pl++) {
-                    tma_load_4d(sm.k[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xk, jt * kTile + hf * kHalf, b, pl);
-                    tma_load_4d(sm.v[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xv, jt * kTile + hf * kHalf, b, pl);
-                }
-            }
-            // Half tile t = 2n + half goes to slot t % 3; a slot is free again once the dV / dK
-            // products that read it have completed.
-            for (int t = 0, slot = 0, use = 0; t < 2 * niter; t++) {
-                if (use >= 1 && !mbar_wait(&sm.in_empty[slot], (use - 1) & 1, ctx, SITE_IN_EMPTY)) break;
+            const int xq = h * kD;
+            // Half tile t = 2n + half goes to slot t % 3 (the first three were requested during
+            // set-up); a slot is free again once the dV / dK products that read it have completed.
+            for (int t = kSlots, slot = 0, use = 1; t < 2 * niter; t++) {
+                if (!mbar_wait(&sm.in_empty[slot], (use - 1) & 1, ctx, SITE_IN_EMPTY)) break;
                 const int y = (jt + (t >> 1)) * kTile + (t & 1) * kHalf;
                 mbar_expect_tx(&sm.in_full[slot], 4 * kPlaneHalf);
                 tma_load_4d(sm.in[slot][0], &map_x, &sm.in_full[slot], xq, y, b, 0);
@@ -315,7 +329,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool kv_stored = false, ok = true;
         uint64_t idle_since = 0;
         uint32_t idle_polls = 0;
-        while (ok && !kv_stored) {
+        while (ok && !(kv_stored && o == niter)) {
             bool progressed = false;
             if (m < niter) {
                 const int buf = m & 1;
@@ -337,20 +351,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         tma_reduce_add_3d(sm.ds[0][0], &map_dx, xq, (jt + o) * kTile, b);
                         tma_reduce_add_3d(sm.ds[0][1], &map_dx, xq + 32, (jt + o) * kTile, b);
                         bulk_commit();
+                        if (o == niter - 1) BWD_EPI2(1);
                         bulk_wait_read_all();
+                        if (o == niter - 1) BWD_EPI2(5);
                         mbar_arrive(&sm.out_free);
                     }
                     __syncwarp();
                     o++;
                     progressed = true;
                 }
-            } else if (__all_sync(0xffffffffu, mbar_test_wait(&sm.kv_out_full, 0))) {
+            }
+            if (!kv_stored && __all_sync(0xffffffffu, mbar_test_wait(&sm.kv_out_full, 0))) {
                 if (lane == 0) {
-                    tma_store_3d(sm.k[0], &map_dx, xk, jt * kTile, b);
-                    tma_store_3d(sm.k[1], &map_dx, xk + 32, jt * kTile, b);
-                    tma_store_3d(sm.v[0], &map_dx, xv, jt * kTile, b);
-                    tma_store_3d(sm.v[1], &map_dx, xv + 32, jt * kTile, b);
+                    tma_store_3d(sm.in[0][0], &map_dx, xk, jt * kTile, b);
+                    tma_store_3d(sm.in[0][2], &map_dx, xk + 32, jt * kTile, b);
+                    tma_store_3d(sm.in[1][0], &map_dx, xv, jt * kTile, b);
+                    tma_store_3d(sm.in[1][2], &map_dx, xv + 32, jt * kTile, b);
                     bulk_commit();
+                    BWD_EPI2(6);
                 }
                 kv_stored = true;
                 progressed = true;
@@ -370,7 +388,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
             }
         }
-        if (lane == 0) bulk_wait_all();  // shared memory must stay alive until the copies have read it
+        // Shared memory must stay alive until the copies have read it; the writes themselves
+        // complete on their own before the grid does.
+        if (lane == 0) bulk_wait_read_all();
+        if (lane == 0) BWD_EPI2(7);
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------ compute group ------------------------------
@@ -480,20 +501,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
         BWD_LIFE(2);
         BWD_EPI(0);
-        if (ok && mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST) &&
-            flush_dq(niter - 1)) {
-            BWD_EPI(2);
-            // The last dQ commit also covers every dV / dK MMA, so K and V in shared memory are dead:
-            // their space stages the dK and dV tiles for the copy engine.
+        // Epilogue.  Once the last dV / dK products have completed the Q/dO ring is dead: its space
+        // stages the dK and dV tiles for the copy engine while the last dQ product still runs.
+        const int last = 2 * niter - 1;
+        if (ok && mbar_wait_warp(&sm.in_empty[last % kSlots], (last / kSlots) & 1, ctx, SITE_IN_EMPTY)) {
+            tc_fence_after_sync();
             uint32_t rk[16], rv[16];
             tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
             tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
             tmem_wait_ld();
             BWD_EPI(3);
-            stage_row(sm.k[0], rk, scale);
-            stage_row(sm.v[0], rv, 1.f);
+            stage_row(sm.in[0][0], rk, scale);
+            stage_row(sm.in[1][0], rv, 1.f);
             fence_proxy_async_smem();
             mbar_arrive(&sm.kv_out_full);
+            BWD_EPI(4);
+            if (mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {
+                flush_dq(niter - 1);
+                BWD_EPI(2);
+            }
         }
     } else if (warp == kGradWarp) {
         // ------------------------------ MMA issuer: dV, dK, dQ ------------------------------
@@ -596,7 +622,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     BWD_EPI(4);
     tc_fence_before_sync();
     __syncthreads();
-    BWD_EPI(5);
     BWD_LIFE(3);
     if (warp == 2) {
         tc_fence_after_sync();
