@@ -205,6 +205,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         mbar_init(&sm.o_full, 1);
         for (int i = 0; i < 4; i++) mbar_init(&sm.pair_bar[i], 64);
         fence_barrier_init();
+        // This thread is also the Q/K producer: Q and the first two K steps are requested right
+        // away, while the other warps are still setting up.
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&map_x);
+        const int xq = h * kD, xk = C + h * kD;
+        mbar_expect_tx(&sm.q_full, 2 * kPlaneTile);
+        for (int hf = 0; hf < 2; hf++) {  // the tensor map's box is 64 rows
+            tma_load_4d(sm.q[0] + hf * kPlaneStep, &map_x, &sm.q_full, xq, qt * kTile + hf * kStep, b, 0);
+            tma_load_4d(sm.q[1] + hf * kPlaneStep, &map_x, &sm.q_full, xq, qt * kTile + hf * kStep, b, 1);
+        }
+        for (int j = 0; j < 2; j++) {  // nsteps >= 2
+            mbar_expect_tx(&sm.k_full[j], 2 * kPlaneStep);
+            tma_load_4d(sm.k[j][0], &map_x, &sm.k_full[j], xk, j * kStep, b, 0);
+            tma_load_4d(sm.k[j][1], &map_x, &sm.k_full[j], xk, j * kStep, b, 1);
+        }
     }
     if (warp == 2) {
         tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -217,18 +232,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
     FWD_LIFE(1);
 
     if (warp == 0) {
-        // ------------------------------ TMA producer: Q, then K ------------------------------
+        // ------------------------------ TMA producer: K ------------------------------
         if (lane == 0) {
-            tma_prefetch_desc(&map_x);
-            const int xq = h * kD, xk = C + h * kD;
-            mbar_expect_tx(&sm.q_full, 2 * kPlaneTile);
-            for (int hf = 0; hf < 2; hf++) {  // the tensor map's box is 64 rows
-                tma_load_4d(sm.q[0] + hf * kPlaneStep, &map_x, &sm.q_full, xq, qt * kTile + hf * kStep, b, 0);
-                tma_load_4d(sm.q[1] + hf * kPlaneStep, &map_x, &sm.q_full, xq, qt * kTile + hf * kStep, b, 1);
-            }
-            for (int j = 0; j < nsteps; j++) {
+            const int xk = C + h * kD;
+            for (int j = 2; j < nsteps; j++) {  // steps 0 and 1 were requested during set-up
                 const int st = j & 1;
-                if (j >= 2 && !mbar_wait(&sm.k_empty[st], ((j >> 1) - 1) & 1, ctx, SITE_K_EMPTY)) break;
+                if (!mbar_wait(&sm.k_empty[st], ((j >> 1) - 1) & 1, ctx, SITE_K_EMPTY)) break;
                 mbar_expect_tx(&sm.k_full[st], 2 * kPlaneStep);
                 tma_load_4d(sm.k[st][0], &map_x, &sm.k_full[st], xk, j * kStep, b, 0);
                 tma_load_4d(sm.k[st][1], &map_x, &sm.k_full[st], xk, j * kStep, b, 1);
@@ -252,6 +261,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
         constexpr uint32_t idesc_o = idesc_bf16_f32(kTile, kD, 0, 1);
         // Q is the A operand of every S = Q K^T of this CTA: the softmax warps copy it once from
         // shared to tensor memory, which halves the shared-memory traffic of those MMAs
+        const uint32_t leader = elect_leader();  // the one lane that issues every MMA and commit
         bool ok = mbar_wait_warp(&sm.q_tmem, 0, ctx, SITE_Q_TMEM);
         // S of step j+1 is issued before the wait for P of step j: the two score buffers alternate,
         // so the tensor cores work on the next scores while the softmax warps are busy.  S_{j+1}
@@ -269,13 +279,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
                 const int qa = term == 2 ? 1 : 0, kb = term == 1 ? 1 : 0;  // hh, hl, lh
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; kk++) {
-                    mma_ts_elect(tmem + kColS + st * kStep, tmem + kColQ + 32 * qa + 8 * kk, desc_advance(kd[kb], kk * 32),
+                    mma_ts_lead(leader, tmem + kColS + st * kStep, tmem + kColQ + 32 * qa + 8 * kk, desc_advance(kd[kb], kk * 32),
                                  idesc_s, acc);
                     acc = 1;
                 }
             }
-            tc_commit_elect(&sm.s_full[st]);
-            tc_commit_elect(&sm.k_empty[st]);
+            tc_commit_lead(leader, &sm.s_full[st]);
+            tc_commit_lead(leader, &sm.k_empty[st]);
             FWD_TRACE(lane == 0, 0, j & 15, 2);
             return true;
         };
@@ -296,13 +306,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
                 const int pa = term == 2 ? 1 : 0, vb = term == 1 ? 1 : 0;  // hh, hl, lh
 #pragma unroll
                 for (int kk = 0; kk < kStep / 16; kk++) {
-                    mma_ts_elect(tmem + kColO, tmem + kColS + st * kStep + 16 * kk + 8 * pa,
+                    mma_ts_lead(leader, tmem + kColO, tmem + kColS + st * kStep + 16 * kk + 8 * pa,
                                  desc_advance(vd[vb], kk * 2048), idesc_o, acc);
                     acc = 1;
                 }
             }
-            tc_commit_elect(&sm.o_full);
-            tc_commit_elect(&sm.v_empty[st]);
+            tc_commit_lead(leader, &sm.o_full);
+            tc_commit_lead(leader, &sm.v_empty[st]);
             FWD_TRACE(lane == 0, 0, j & 15, 4);
         }
     } else if (warp >= 4) {
