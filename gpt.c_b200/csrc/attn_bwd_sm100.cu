@@ -8,32 +8,42 @@
 // One CTA owns one (batch, head) and one tile of 128 keys (K_j, V_j stay in shared memory) and
 // walks the query tiles i = j .. last.  Everything is computed transposed so that the key index
 // is the tensor-memory lane:
-//     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (SS, all operands K-major)
+//     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (B = Q / dO half, K-major)
 //     P^T  = exp2(S^T * c - lse_i)        dS^T = P^T * (dP^T - delta_i)      (one thread per key)
 //     dV_j += P^T dO_i            dK_j += dS^T Q_i                  (A from tensor memory)
 //     dQ_i  = dS K_j                                                (A = dS^T tile in shared
 //                                                                    memory read MN-major)
-// dK_j and dV_j accumulate in tensor memory over the whole loop and are written once; dQ_i is
-// added into the (zeroed) dq third of the output with fp32 atomics, since other key tiles
-// contribute to the same rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
+// dK_j and dV_j accumulate in tensor memory over the whole loop and leave once through bulk
+// tensor stores; dQ_i is staged as an fp32 tile in shared memory and added into the (zeroed) dq
+// third of the output by bulk tensor reductions, since other key tiles contribute to the same
+// rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
 //
 // Each query tile is processed as two halves of 64 queries (A, B) with their own barriers, so the
 // tensor cores and the compute warps overlap: while the compute warps turn S^T/dP^T of half B
-// into P^T/dS^T, the tensor cores already run dV/dK of half A, and the next tile's S^T of half A
-// can be issued as soon as its Q/dO half has landed and the columns it overwrites were consumed.
+// into P^T/dS^T, the tensor cores already run dV/dK of half A, the previous tile's dQ and the
+// next tile's scores.
 //
-// Warp roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (the whole warp runs the
-// issue loop, one elected lane issues; whichever task is ready goes first), warp 2 tensor-memory
-// allocation, warps 4-19 compute.  A compute warp's quarter (warp % 4) selects the 32
-// tensor-memory lanes it may touch (keys for S^T / dP^T / dK / dV, queries for dQ); its column
-// group (0..3) selects 16 of the 64 query columns of a half and 16 of the 64 columns of
-// dQ / dK / dV.
+// Warp roles (640 threads):
+//   warp 0      TMA producer: K, V once; Q/dO half tiles through a ring of three slots
+//   warp 1      issues the score MMAs (S^T, dP^T), in order
+//   warp 2      allocates tensor memory; stages the row statistics (-lse, -delta) of every query
+//               tile; drives the output copies (dQ reductions, final dK / dV stores)
+//   warp 3      issues the gradient MMAs (dV, dK per half; dQ per tile), whichever is ready first
+//   warps 4-19  compute.  A compute warp's quarter (warp % 4) selects the 32 tensor-memory lanes
+//               it may touch (keys for S^T / dP^T / dK / dV, queries for dQ); its column group
+//               (0..3) selects 16 of the 64 query columns of a half and 16 of the 64 columns of
+//               dQ / dK / dV.
+// Two issuing warps on two schedulers, each electing its issuing lane once: a single issuing warp
+// competes with four busy compute warps for its scheduler's issue slots and feeds the tensor pipe
+// at well under its rate.  Dependencies between the two (a score task overwrites the columns a
+// gradient task read) go through completion barriers, not through issue order.
 //
 // Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448)
 // K hi [448,480)  V hi [480,512).  The hi planes of K and V are copied there once so that two of
-// the three terms of S^T and dP^T take their A operand from tensor memory: shared-memory
-// bandwidth, not the tensor pipe, is what limits this kernel.  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes
-// 8 columns of packed bf16 hi parts followed by 8 columns of packed lo parts.
+// the three terms of S^T and dP^T take their A operand from tensor memory: an MMA with both
+// operands in shared memory is limited by shared-memory bandwidth (48 instead of 32 cycles at
+// N = 64).  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes 8 columns
+// of packed bf16 hi parts followed by 8 columns of packed lo parts.
 #include "attn_internal.h"
 #include "tc05.cuh"
 
