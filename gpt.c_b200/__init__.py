@@ -33,6 +33,7 @@ SIGNATURES = {
     "attn_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 5 + [_c.c_void_p]),
     "attn_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 5 + [_c.c_void_p]),
     "attn_sm100_forward_static": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 4 + [_c.c_void_p]),
+    "attn_sm100_selftest_wait_limit": (_c.c_int, [_c.c_uint, _c.c_void_p]),
     "attn_sm100_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
 }

@@ -2,6 +2,7 @@
 // and kernel dispatch.  Declarations and the reference interfaces they replace are in
 // include/attn_sm100.h.
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 #include <math.h>
 #include <stdio.h>
@@ -72,6 +73,24 @@ int current_device_state(DeviceState **out) {
     }
     *out = &g_dev[dev];
     return ATTN_OK;
+}
+
+
+// Exercises the bounded-wait path every tcgen05 kernel relies on, without touching the tensor
+// cores: the barrier below is never completed, so the wait runs out after `limit_ns`, records
+// ST_TIMEOUT_BASE + 900 in the status word and the kernel returns normally.
+constexpr int kSelftestSite = 900;
+__global__ void wait_limit_selftest_kernel(int *status, unsigned long long limit_ns) {
+    __shared__ uint64_t never;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        tc05::mbar_init(&never, 1);
+        tc05::fence_barrier_init();
+    }
+    __syncthreads();
+    tc05::WaitCtx ctx{&abort_flag, status, limit_ns};
+    tc05::mbar_wait_warp(&never, 0, ctx, kSelftestSite);
 }
 
 }  // namespace
@@ -203,6 +222,15 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
         e = attn::launch_generic_backward(xhi, xlo, lse, delta, dout, dqkv, B, T, H, D, s);
     }
     return (int)e;
+}
+
+int attn_sm100_selftest_wait_limit(unsigned limit_us, void *stream) {
+    if (limit_us == 0 || limit_us > 100000u) return ATTN_ERR_SHAPE;  // at most 0.1 s
+    DeviceState *ds = nullptr;
+    const int rc = current_device_state(&ds);
+    if (rc != ATTN_OK) return rc;
+    wait_limit_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(ds->status, (unsigned long long)limit_us * 1000ull);
+    return (int)cudaGetLastError();
 }
 
 int attn_sm100_device_status(int *status, int clear) {

@@ -92,6 +92,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
 struct WaitCtx {
     volatile int *cta_abort;  // shared memory
     int *status;              // global memory, may be nullptr
+    uint64_t limit_ns;        // 0: TC05_WAIT_LIMIT_NS
 };
 
 #ifndef TC05_WAIT_LIMIT_NS
@@ -102,12 +103,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if (*ctx.cta_abort) return false;
     const uint64_t t0 = global_timer_ns();
+    const uint64_t limit = ctx.limit_ns ? ctx.limit_ns : TC05_WAIT_LIMIT_NS;
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++it & 63u) == 0u) {
             if (*ctx.cta_abort) return false;
-            if (global_timer_ns() - t0 > TC05_WAIT_LIMIT_NS) break;
+            if (global_timer_ns() - t0 > limit) break;
         }
     }
     *ctx.cta_abort = 1;

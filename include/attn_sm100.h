@@ -147,6 +147,17 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
 int attn_sm100_forward_static(const float *qkv, float *out, float *lse, int B, int T, int H, int D, void *stream);
 
 /*
+ * Failure-path self-test (no counterpart in the reference, which has no bounded waits): launches a
+ * one-CTA kernel that waits, with the same helper every tcgen05 kernel of this library uses, on a
+ * barrier that is never completed.  After `limit_us` microseconds (1..100000) the wait gives up,
+ * the kernel returns normally and the device status word holds 1900; attn_sm100_device_status then
+ * returns ATTN_ERR_KERNEL until the word is cleared.  Nothing faults, traps or spins for ever, and
+ * the context stays usable.  Returns ATTN_OK when the kernel was enqueued, ATTN_ERR_SHAPE for a
+ * limit outside the range, or a cudaError_t.
+ */
+int attn_sm100_selftest_wait_limit(unsigned limit_us, void *stream);
+
+/*
  * Synchronises the current device and reads its status word.  *status receives 0, or a code
  * >= 1000 naming the bounded wait that ran out inside a kernel.  When `clear` is non-zero the
  * word is reset.  Returns ATTN_OK, ATTN_ERR_KERNEL when *status != 0, or a cudaError_t.
