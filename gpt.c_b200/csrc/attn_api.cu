@@ -169,7 +169,15 @@ int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse
         CUtensorMap map_x;
         rc = encode_planes(&map_x, saved, B, T, 3 * H * D, plane, 64);
         if (rc != 0) return rc;
-        e = attn::launch_fast_forward(map_x, out, out_copy, lse, B, T, H, ds->status, s);
+        CUtensorMap map_out, map_copy;
+        rc = encode_rows_f32(&map_out, out, B, T, H * D);
+        if (rc != 0) return rc;
+        if (out_copy) {
+            rc = encode_rows_f32(&map_copy, out_copy, B, T, H * D);
+            if (rc != 0) return rc;
+        }
+        e = attn::launch_fast_forward(map_x, &map_out, out_copy ? &map_copy : nullptr, out, out_copy, lse, B, T, H,
+                                      ds->status, s);
     } else {
         e = attn::launch_generic_forward(qkv, out, out_copy, lse, B, T, H, D, s);
     }

@@ -55,6 +55,7 @@ struct __align__(1024) FwdSmem {
     uint8_t v[2][2][kPlaneStep];
     uint64_t q_full, q_tmem, k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t s_full[2], p_full[2], o_full;
+    uint64_t epi_bar;           // every softmax thread has staged its part of the output tile
     uint64_t pair_bar[4];       // [quarter]: the two halves of a row block meet here once per tile
     float xmax[2][2][kTile];    // [tile parity][half][row]: row maxima exchanged between halves
     float lpart[2][kTile];      // [half][row]: partial row sums for the epilogue
@@ -64,7 +65,7 @@ struct __align__(1024) FwdSmem {
 
 enum Site : int {
     SITE_K_EMPTY = 1, SITE_V_EMPTY, SITE_Q_FULL, SITE_K_FULL, SITE_V_FULL, SITE_P_FULL, SITE_S_FULL, SITE_O_FULL,
-    SITE_O_FULL_LAST, SITE_PAIR, SITE_Q_TMEM
+    SITE_O_FULL_LAST, SITE_PAIR, SITE_Q_TMEM, SITE_EPI_BAR
 };
 
 // Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
@@ -172,8 +173,9 @@ __device__ __forceinline__ float exp_pass(uint32_t t_s, int row, int half, int k
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ out, float *__restrict__ out_copy,
-                float *__restrict__ lse, int B, int T, int H, float scale_log2, int *status) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_out,
+                const __grid_constant__ CUtensorMap map_copy, int out_maps, float *__restrict__ out,
+                float *__restrict__ out_copy, float *__restrict__ lse, int B, int T, int H, float scale_log2, int *status) {
     extern __shared__ uint8_t smem_raw[];
     FwdSmem &sm = *reinterpret_cast<FwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -203,6 +205,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
             mbar_init(&sm.p_full[i], kSoftmaxThreads);
         }
         mbar_init(&sm.o_full, 1);
+        mbar_init(&sm.epi_bar, kSoftmaxThreads);
         for (int i = 0; i < 4; i++) mbar_init(&sm.pair_bar[i], 64);
         fence_barrier_init();
         // This thread is also the Q/K producer: Q and the first two K steps are requested right
@@ -399,7 +402,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
             const float l_all = sm.lpart[0][row] + sm.lpart[1][row];
             const float inv = 1.0f / l_all;
             const int t = qt * kTile + row;
-            if (t < T) {
+            if (t < T && half == 0) lse[(size_t)bh * T + t] = (m + __log2f(l_all)) * 0.6931471805599453f;
+            if (out_maps > 0) {
+                // The normalised tile leaves through the copy engine: this thread's 32 columns are one
+                // 128-byte row of a [128 x 32] fp32 box, staged (16-byte chunks swizzled by row % 8) in
+                // the space of the Q tile, which has been dead since Q went to tensor memory.  Rows
+                // past the end of the sequence are dropped by the copy engine.
+                uint8_t *base = sm.q[half] + row * 128;
+#pragma unroll
+                for (int d4 = 0; d4 < 8; d4++)
+                    *reinterpret_cast<float4 *>(base + ((d4 ^ (row & 7)) << 4)) =
+                        make_float4(__uint_as_float(r[4 * d4]) * inv, __uint_as_float(r[4 * d4 + 1]) * inv,
+                                    __uint_as_float(r[4 * d4 + 2]) * inv, __uint_as_float(r[4 * d4 + 3]) * inv);
+                fence_proxy_async_smem();
+                mbar_arrive(&sm.epi_bar);
+                if (threadIdx.x == 128 && mbar_wait(&sm.epi_bar, 0, ctx, SITE_EPI_BAR)) {
+                    tma_store_3d(sm.q[0], &map_out, h * kD, qt * kTile, b);
+                    tma_store_3d(sm.q[1], &map_out, h * kD + 32, qt * kTile, b);
+                    if (out_maps > 1) {
+                        tma_store_3d(sm.q[0], &map_copy, h * kD, qt * kTile, b);
+                        tma_store_3d(sm.q[1], &map_copy, h * kD + 32, qt * kTile, b);
+                    }
+                    bulk_commit();
+                    bulk_wait_read_all();  // shared memory must stay alive until the copies have read it
+                }
+            } else if (t < T) {
                 const size_t o_off = ((size_t)b * T + t) * C + (size_t)h * kD + 32 * half;
                 float4 *dst = reinterpret_cast<float4 *>(out + o_off);
                 float4 *dst2 = out_copy ? reinterpret_cast<float4 *>(out_copy + o_off) : nullptr;
@@ -410,7 +437,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, float *__restrict__ o
                     dst[d4] = f;
                     if (dst2) dst2[d4] = f;
                 }
-                if (half == 0) lse[(size_t)bh * T + t] = (m + __log2f(l_all)) * 0.6931471805599453f;
             }
         }
     }
@@ -441,12 +467,18 @@ cudaError_t fast_fwd_set_attributes() {
     return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem_bytes());
 }
 
-cudaError_t launch_fast_forward(const CUtensorMap &map_x, float *out, float *out_copy, float *lse, int B, int T, int H,
-                                int *status, cudaStream_t s) {
+// map_out / map_copy: fp32 {C, T, B} maps of out / out_copy with boxes of 32 columns x 128 rows and
+// 128-byte swizzle; with map_out == nullptr the kernel writes out (and out_copy) with plain stores.
+cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map_out, const CUtensorMap *map_copy,
+                                float *out, float *out_copy, float *lse, int B, int T, int H, int *status, cudaStream_t s) {
     const int nqt = (T + kTile - 1) / kTile;
     const unsigned grid = (unsigned)(nqt * B * H);
     const float scale_log2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
-    attn_fwd_kernel<<<grid, kThreads, fwd_smem_bytes(), s>>>(map_x, out, out_copy, lse, B, T, H, scale_log2, status);
+    const int out_maps = map_out ? (map_copy && out_copy ? 2 : 1) : 0;
+    const CUtensorMap &mo = map_out ? *map_out : map_x;  // unused by the kernel when out_maps == 0
+    const CUtensorMap &mc = out_maps == 2 ? *map_copy : mo;
+    attn_fwd_kernel<<<grid, kThreads, fwd_smem_bytes(), s>>>(map_x, mo, mc, out_maps, out, out_copy, lse, B, T, H,
+                                                             scale_log2, status);
     return cudaGetLastError();
 }
 

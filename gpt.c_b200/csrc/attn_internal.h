@@ -39,8 +39,8 @@ cudaError_t launch_generic_backward(const __nv_bfloat16 *xhi, const __nv_bfloat1
 //   map_do: dims { C, T, B, 2 planes}, same box
 cudaError_t fast_fwd_set_attributes();
 cudaError_t fast_bwd_set_attributes();
-cudaError_t launch_fast_forward(const CUtensorMap &map_x, float *out, float *out_copy, float *lse, int B, int T, int H,
-                                int *status, cudaStream_t s);
+cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map_out, const CUtensorMap *map_copy,
+                                float *out, float *out_copy, float *lse, int B, int T, int H, int *status, cudaStream_t s);
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
                                  const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s);
 

@@ -105,5 +105,5 @@ extern "C" int attn_sm100_forward_static(const float *qkv, float *out, float *ls
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return (int)cudaErrorInvalidValue;
-    return (int)attn::launch_fast_forward(map_x, out, nullptr, lse, B, T, H, st.status, s);
+    return (int)attn::launch_fast_forward(map_x, nullptr, nullptr, out, nullptr, lse, B, T, H, st.status, s);
 }
