@@ -13,7 +13,8 @@ Printed JSON line (rank 0):
   value      whole-job algorithmic TFLOP/s (6*B*H*T^2*D / 2 per pass, causal count) with inputs
              resident in HBM, CUDA-event time, max over ranks
   e2e        the same metric through the C ABI with pinned HOST buffers: the H2D copy of qkv and
-             dout and the D2H copy of out and dqkv are inside the timed region
+             dout and the D2H copy of out and dqkv are inside the timed region, every step; upload,
+             kernels and download run on three event-chained streams so consecutive steps overlap
   roofline   the dominant kernel (backward core) timed live with CUDA events
   cpu_baseline  the reference's own CPU attention (OpenBLAS) on this box's host cores, rank 0, N=1
 
@@ -308,22 +309,48 @@ def run_ours(args):
     stage_ms = [statistics.mean(ev[i][k].elapsed_time(ev[i][k + 1]) for i in range(args.steps)) for k in range(4)]
 
     # ---------------- end-to-end through the C ABI with host buffers ----------------
+    # Every step copies its qkv and dout from pinned host memory, runs forward + backward through the
+    # C ABI and copies out and dqkv back to pinned host memory.  The three legs run on three streams
+    # chained by events, so the upload of step i+1 and the download of step i-1 overlap the kernels of
+    # step i (PCIe is full duplex); a buffer set is reused only after its previous download finished.
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    in_done = [torch.cuda.Event() for _ in range(ROTATE)]
+    comp_done = [torch.cuda.Event() for _ in range(ROTATE)]
+    out_done = [torch.cuda.Event() for _ in range(ROTATE)]
+
     def e2e_step(i):
-        s = sets[i % ROTATE]
-        s["x"].copy_(x_pin, non_blocking=True)
-        s["g"].copy_(g_pin, non_blocking=True)
-        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H)
-        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H)
-        out_pin.copy_(s["out"], non_blocking=True)
-        dx_pin.copy_(s["dx"], non_blocking=True)
+        k = i % ROTATE
+        s = sets[k]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(comp_done[k])  # the kernels that last read this set's inputs
+            s["x"].copy_(x_pin, non_blocking=True)
+            s["g"].copy_(g_pin, non_blocking=True)
+            in_done[k].record(s_in)
+        stream.wait_event(in_done[k])
+        stream.wait_event(out_done[k])  # the download that last read this set's outputs
+        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, stream=stream)
+        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, stream=stream)
+        comp_done[k].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[k])
+            out_pin.copy_(s["out"], non_blocking=True)
+            dx_pin.copy_(s["dx"], non_blocking=True)
+            out_done[k].record(s_out)
+
+    def e2e_join():
+        stream.wait_stream(s_in)
+        stream.wait_stream(s_out)
 
     for i in range(args.warmup):
         e2e_step(i)
+    e2e_join()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
+    s_in.wait_event(e0)
     for i in range(args.steps):
         e2e_step(i)
+    e2e_join()
     e1.record(stream)
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
