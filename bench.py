@@ -45,7 +45,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 ROTATE = 4  # buffer sets cycled through so that a set is evicted from L2 before it is reused
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the
 # bench workload, from the ncu capture summarised under profiles/ (None until captured)
-BWD_CORE_DRAM_BYTES = 190307840  # profiles/ncu_full_attention_B8_T1024_H12.txt
+BWD_CORE_DRAM_BYTES = 191820288  # profiles/ncu_full_attention_B8_T1024_H12.txt
 
 
 def flops_fwd(B, T, H, D):
@@ -371,6 +371,10 @@ def run_ours(args):
         "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": BWD_CORE_DRAM_BYTES,
         "peak_source": peaks["source"] + " (cuBLAS bf16, sustained)",
         "launch_us": stage_ms[3] * 1e3,
+        # what the tensor pipe really executes: S is recomputed (5 products for 4 algorithmic ones) and
+        # every product is three bf16 passes (hi*hi + hi*lo + lo*hi)
+        "executed": {"tflops": achieved * 15.0 / 4.0, "frac": achieved * 15.0 / 4.0 / peak_tf,
+                     "passes_per_algorithmic_product": 3.75},
         "hbm": {"achieved_gbs": ab["bwd"] / bwd_core_s / 1e9, "peak_gbs": peaks["hbm_gbs"],
                 "frac": ab["bwd"] / bwd_core_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": ab["bwd"]},
     }
