@@ -15,6 +15,10 @@ Printed JSON line (rank 0):
   e2e        the same metric through the C ABI with pinned HOST buffers: the H2D copy of qkv and
              dout and the D2H copy of out and dqkv are inside the timed region, every step; upload,
              kernels and download run on three event-chained streams so consecutive steps overlap
+  stage_us   launch duration of each of the four kernels, from a second pass over the same K steps
+             with an event between the kernels (those events idle the GPU for a few microseconds
+             each, so the headline pass runs without them)
+  graph      the same K steps replayed from CUDA graphs (one per buffer set): no host in the loop
   roofline   the dominant kernel (backward core) timed live with CUDA events
   cpu_baseline  the reference's own CPU attention (OpenBLAS) on this box's host cores, rank 0, N=1
 
@@ -36,7 +40,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-WORKLOAD = {"B": 8, "T": 1024, "H": 12, "D": 64}
+# The default is the configuration the metric is quoted on; the others are the remaining shapes of the
+# reference's configuration list, selectable with --workload for per-configuration tables.
+WORKLOADS = {
+    "gpt2-124M-T1024": {"B": 8, "T": 1024, "H": 12, "D": 64, "backward": True},     # the benchmark line
+    "gpt2-124M-T128": {"B": 8, "T": 128, "H": 12, "D": 64, "backward": True},
+    "gpt2-medium-fwd": {"B": 32, "T": 1024, "H": 16, "D": 64, "backward": False},   # forward only
+    "gpt2-xl-B64": {"B": 64, "T": 1024, "H": 25, "D": 64, "backward": True},
+}
+DEFAULT_WORKLOAD = "gpt2-124M-T1024"
+WORKLOAD = dict(WORKLOADS[DEFAULT_WORKLOAD])
 SEED = 1234
 METRIC = "attn fwd+bwd TFLOP/s"
 UNIT = "TFLOP/s"
@@ -132,10 +145,12 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
-def seeded_host_inputs(rank: int):
+def seeded_host_inputs(rank: int, batch: int | None = None):
     import numpy as np
 
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    if batch is not None:
+        B = min(B, batch)
     rng = np.random.default_rng(SEED + rank)
     x = rng.standard_normal((B, T, 3 * H * D), dtype=np.float32)
     g = rng.standard_normal((B, T, H * D), dtype=np.float32)
@@ -176,8 +191,7 @@ def run_reference_arm(args):
         return  # rank 0 alone measures the host cores
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
     sample_b = 2
-    x, g = seeded_host_inputs(0)
-    x, g = x[:sample_b].copy(), g[:sample_b].copy()
+    x, g = seeded_host_inputs(0, sample_b)
     kind, run, info = cpu_attention_runner()
     for _ in range(args.warmup):
         run(x, g, H)
@@ -189,7 +203,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "causal attention fwd+bwd B=8 T=1024 H=12 D=64 fp32 io", "sample_batch": sample_b,
+        "config": {"workload": f"causal attention fwd+bwd B={B} T={T} H={H} D={D} fp32 io", "sample_batch": sample_b,
                    "seed": SEED},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": kind,
                          "sample": f"{sample_b} of {B} batch entries per step, fwd+bwd, {args.steps} steps",
@@ -202,12 +216,14 @@ def run_reference_arm(args):
 
 def measure_cpu_baseline():
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
-    x, g = seeded_host_inputs(0)
+    sample_b = min(B, 8)  # bounded: the largest configurations would take minutes on the host
+    x, g = seeded_host_inputs(0, sample_b)
     kind, run, info = cpu_attention_runner()
-    secs = run(x, g, H)  # one full pass of the workload
-    fl = flops_fwd(B, T, H, D) + flops_bwd(B, T, H, D)
+    secs = run(x, g, H)  # forward + backward of the sample (the CPU kernels are timed as a pair)
+    fl = flops_fwd(sample_b, T, H, D) + flops_bwd(sample_b, T, H, D)
+    what = "the full workload" if sample_b == B else f"{sample_b} of {B} batch entries"
     return {"value": fl / secs / 1e12, "unit": UNIT, "cores": info["cores"], "kind": kind,
-            "sample": f"one fwd+bwd pass of the full workload (B={B}), {secs:.2f} s", "blas": info["blas"]}
+            "sample": f"one fwd+bwd pass of {what} (B={sample_b}), {secs:.2f} s", "blas": info["blas"]}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -231,6 +247,7 @@ def run_ours(args):
     pkg = entry.load_package()
     pkg.init()
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    with_bwd = WORKLOAD["backward"]
     C = H * D
     dev = torch.device("cuda", local_rank)
     xh, gh = seeded_host_inputs(rank)
@@ -239,20 +256,31 @@ def run_ours(args):
     out_pin = torch.empty((B, T, C), dtype=torch.float32).pin_memory()
     dx_pin = torch.empty((B, T, 3 * C), dtype=torch.float32).pin_memory()
 
-    sets = []
-    for _ in range(ROTATE):
-        sets.append({
+    def make_set():
+        return {
             "x": x_pin.to(dev), "g": g_pin.to(dev),
             "out": torch.empty((B, T, C), device=dev), "lse": torch.empty((B, H, T), device=dev),
             "saved": torch.empty(pkg.saved_bytes(B, T, H, D), device=dev, dtype=torch.uint8),
             "scratch": torch.empty(pkg.backward_scratch_bytes(B, T, H, D), device=dev, dtype=torch.uint8),
             "dx": torch.empty((B, T, 3 * C), device=dev),
-        })
+        }
+
+    sets = [make_set()]
     set_bytes = sum(t.numel() * t.element_size() for t in sets[0].values())
+    # enough sets that the others together exceed twice the L2 before one is reused
+    rotate = max(ROTATE, int(2 * 126e6 // set_bytes) + 2)
+    while len(sets) < rotate:
+        sets.append(make_set())
     stream = torch.cuda.current_stream()
 
     def step(i, events=None):
-        s = sets[i % ROTATE]
+        s = sets[i % rotate]
+        if events is None:  # the calls a user makes: one forward, one backward
+            pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H)
+            if with_bwd:
+                pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H)
+            return
+        # staged variant: the same four kernels launched one by one with an event between them
         if events is not None:
             events[0].record(stream)
         pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_PREPARE_ONLY)
@@ -261,10 +289,12 @@ def run_ours(args):
         pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_CORE_ONLY)
         if events is not None:
             events[2].record(stream)
-        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_PREPARE_ONLY)
+        if with_bwd:
+            pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_PREPARE_ONLY)
         if events is not None:
             events[3].record(stream)
-        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_CORE_ONLY)
+        if with_bwd:
+            pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_CORE_ONLY)
         if events is not None:
             events[4].record(stream)
 
@@ -291,22 +321,66 @@ def run_ours(args):
     # ---------------- device-resident timed region ----------------
     for i in range(args.warmup):
         step(i)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(physical_gpu_index(local_rank))
     barrier()
     sampler.start()
     t0.record(stream)
     for i in range(args.steps):
-        step(i, ev[i])
+        step(i)
     t1.record(stream)
     barrier()
-    clocks = sampler.stop()
     ms_total = max_over_ranks(t0.elapsed_time(t1))
+    # Second timed pass over the same K steps with an event between the kernels: it gives the launch
+    # duration of each kernel (the roofline uses the backward core's).  The events cost a few
+    # microseconds of idle GPU each, which is why the headline pass above runs without them.
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s0.record(stream)
+    for i in range(args.steps):
+        step(i, ev[i])
+    s1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    staged_ms_total = max_over_ranks(s0.elapsed_time(s1))
     status = pkg.device_status()
     if status != 0:
         raise SystemExit(f"kernel status word {status}: a bounded wait ran out")
     stage_ms = [statistics.mean(ev[i][k].elapsed_time(ev[i][k + 1]) for i in range(args.steps)) for k in range(4)]
+
+    # ---------------- optional: the same steps replayed from CUDA graphs ----------------
+    # For short sequences the four launches of a step take less GPU time than the host needs to issue
+    # them; one captured graph per buffer set removes the host from the loop.
+    graph_info = None
+    if args.graph:
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            for k in range(rotate):
+                gr = torch.cuda.CUDAGraph()
+                s_k = sets[k]
+                with torch.cuda.graph(gr, stream=side):
+                    pkg.forward_into(s_k["x"], s_k["out"], None, s_k["lse"], s_k["saved"], H, stream=side)
+                    if with_bwd:
+                        pkg.backward_into(s_k["saved"], s_k["out"], s_k["lse"], s_k["g"], s_k["dx"], s_k["scratch"], H,
+                                          stream=side)
+                graphs.append(gr)
+        stream.wait_stream(side)
+        for i in range(args.warmup):
+            graphs[i % rotate].replay()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record(stream)
+        for i in range(args.steps):
+            graphs[i % rotate].replay()
+        g1.record(stream)
+        barrier()
+        graph_ms = max_over_ranks(g0.elapsed_time(g1))
+        if pkg.device_status() != 0:
+            raise SystemExit("kernel status word set during graph replay")
+        graph_info = {"ms_per_step": graph_ms / args.steps}
 
     # ---------------- end-to-end through the C ABI with host buffers ----------------
     # Every step copies its qkv and dout from pinned host memory, runs forward + backward through the
@@ -314,27 +388,30 @@ def run_ours(args):
     # chained by events, so the upload of step i+1 and the download of step i-1 overlap the kernels of
     # step i (PCIe is full duplex); a buffer set is reused only after its previous download finished.
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    in_done = [torch.cuda.Event() for _ in range(ROTATE)]
-    comp_done = [torch.cuda.Event() for _ in range(ROTATE)]
-    out_done = [torch.cuda.Event() for _ in range(ROTATE)]
+    in_done = [torch.cuda.Event() for _ in range(rotate)]
+    comp_done = [torch.cuda.Event() for _ in range(rotate)]
+    out_done = [torch.cuda.Event() for _ in range(rotate)]
 
     def e2e_step(i):
-        k = i % ROTATE
+        k = i % rotate
         s = sets[k]
         with torch.cuda.stream(s_in):
             s_in.wait_event(comp_done[k])  # the kernels that last read this set's inputs
             s["x"].copy_(x_pin, non_blocking=True)
-            s["g"].copy_(g_pin, non_blocking=True)
+            if with_bwd:
+                s["g"].copy_(g_pin, non_blocking=True)
             in_done[k].record(s_in)
         stream.wait_event(in_done[k])
         stream.wait_event(out_done[k])  # the download that last read this set's outputs
         pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, stream=stream)
-        pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, stream=stream)
+        if with_bwd:
+            pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, stream=stream)
         comp_done[k].record(stream)
         with torch.cuda.stream(s_out):
             s_out.wait_event(comp_done[k])
             out_pin.copy_(s["out"], non_blocking=True)
-            dx_pin.copy_(s["dx"], non_blocking=True)
+            if with_bwd:
+                dx_pin.copy_(s["dx"], non_blocking=True)
             out_done[k].record(s_out)
 
     def e2e_join():
@@ -355,28 +432,35 @@ def run_ours(args):
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
 
-    flops_step = flops_fwd(B, T, H, D) + flops_bwd(B, T, H, D)
+    flops_step = flops_fwd(B, T, H, D) + (flops_bwd(B, T, H, D) if with_bwd else 0.0)
     value = flops_step * world * args.steps / (ms_total * 1e-3) / 1e12
     e2e_value = flops_step * world * args.steps / (e2e_ms * 1e-3) / 1e12
-    h2d = x_pin.numel() * 4 + g_pin.numel() * 4
-    d2h = out_pin.numel() * 4 + dx_pin.numel() * 4
+    h2d = x_pin.numel() * 4 + (g_pin.numel() * 4 if with_bwd else 0)
+    d2h = out_pin.numel() * 4 + (dx_pin.numel() * 4 if with_bwd else 0)
 
     peaks = load_peaks()
-    bwd_core_s = stage_ms[3] * 1e-3
-    achieved = flops_bwd(B, T, H, D) / bwd_core_s / 1e12
     peak_tf = peaks["bf16_tflops_sustained"]
     ab = algorithmic_bytes(B, T, H, D)
+    is_default = all(WORKLOAD[k] == WORKLOADS[DEFAULT_WORKLOAD][k] for k in WORKLOAD)
+    if with_bwd:
+        # dominant kernel: the backward core.  The tensor pipe really executes 15 passes per 4
+        # algorithmic products: S is recomputed (5 products) and every product is three bf16 passes.
+        core_s, core_fl, core_bytes, passes = stage_ms[3] * 1e-3, flops_bwd(B, T, H, D), ab["bwd"], 15.0 / 4.0
+        kernel_name = "attn_bwd_kernel (backward core)"
+    else:
+        core_s, core_fl, core_bytes, passes = stage_ms[1] * 1e-3, flops_fwd(B, T, H, D), ab["fwd"], 3.0
+        kernel_name = "attn_fwd_kernel (forward core)"
+    achieved = core_fl / core_s / 1e12
     roofline = {
-        "kernel": "attn_bwd_kernel (backward core)", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
-        "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": BWD_CORE_DRAM_BYTES,
+        "kernel": kernel_name, "bound": "tensor", "achieved": achieved, "peak": peak_tf,
+        "unit": "TFLOP/s", "frac": achieved / peak_tf,
+        "traffic": BWD_CORE_DRAM_BYTES if (with_bwd and is_default) else None,
         "peak_source": peaks["source"] + " (cuBLAS bf16, sustained)",
-        "launch_us": stage_ms[3] * 1e3,
-        # what the tensor pipe really executes: S is recomputed (5 products for 4 algorithmic ones) and
-        # every product is three bf16 passes (hi*hi + hi*lo + lo*hi)
-        "executed": {"tflops": achieved * 15.0 / 4.0, "frac": achieved * 15.0 / 4.0 / peak_tf,
-                     "passes_per_algorithmic_product": 3.75},
-        "hbm": {"achieved_gbs": ab["bwd"] / bwd_core_s / 1e9, "peak_gbs": peaks["hbm_gbs"],
-                "frac": ab["bwd"] / bwd_core_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": ab["bwd"]},
+        "launch_us": core_s * 1e6,
+        "executed": {"tflops": achieved * passes, "frac": achieved * passes / peak_tf,
+                     "passes_per_algorithmic_product": passes},
+        "hbm": {"achieved_gbs": core_bytes / core_s / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                "frac": core_bytes / core_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": core_bytes},
     }
 
     cpu_baseline = None
@@ -385,24 +469,29 @@ def run_ours(args):
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if with_bwd else "attn fwd TFLOP/s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
-                "workload": "causal attention fwd+bwd, fused qkv [B,T,3C] fp32 io, B=8 T=1024 H=12 D=64 per GPU",
+                "workload": f"causal attention {'fwd+bwd' if with_bwd else 'fwd only'}, fused qkv [B,T,3C] fp32 io, "
+                            f"B={B} T={T} H={H} D={D} per GPU",
+                "name": args.workload,
                 "global_batch": B * world, "seq_len": T, "n_heads": H, "head_dim": D, "seed": SEED,
                 "precision": "bf16 hi/lo split operands (3 MMAs per product), fp32 accumulate and softmax",
-                "l2": f"{ROTATE} rotating buffer sets of {set_bytes / 1e6:.0f} MB each (> 126 MB L2 between reuses)",
+                "l2": f"{rotate} rotating buffer sets of {set_bytes / 1e6:.0f} MB each (> 126 MB L2 between reuses)",
                 "parallelism": f"batch shards on {world} GPU(s), no collective",
             },
             "pct_of_nominal_bf16_peak": 100.0 * value / (NOMINAL_BF16_TFLOPS * world),
             "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops_sustained"] * world),
+            "staged_pass_ms_per_step": staged_ms_total / args.steps,
             "stage_us": {"fwd_split": stage_ms[0] * 1e3, "fwd_core": stage_ms[1] * 1e3,
                          "bwd_prepare": stage_ms[2] * 1e3, "bwd_core": stage_ms[3] * 1e3},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": (4 if with_bwd else 2) * args.steps,
             "clocks": clocks,
+            "graph": (graph_info | {"value": flops_step * world / (graph_info["ms_per_step"] * 1e-3) / 1e12,
+                                    "unit": UNIT}) if graph_info else None,
             "roofline": roofline,
             "cpu_baseline": cpu_baseline,
         }
@@ -419,7 +508,13 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
     ap.add_argument("--no-ramp", action="store_true", help="skip the untimed clock ramp (for profiler captures)")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="skip the extra pass that replays the steps from CUDA graphs (one per buffer set)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD,
+                    help="shape to run; the default is the one the metric is quoted on")
     args = ap.parse_args()
+    WORKLOAD.clear()
+    WORKLOAD.update(WORKLOADS[args.workload])
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
