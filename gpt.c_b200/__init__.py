@@ -36,6 +36,8 @@ SIGNATURES = {
     "attn_sm100_selftest_wait_limit": (_c.c_int, [_c.c_uint, _c.c_void_p]),
     "attn_sm100_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
+    "linear_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
+    "linear_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 3 + [_c.c_void_p]),
 }
 
 _lib = None
@@ -152,3 +154,36 @@ def backward(ctx: Saved, dout):
     scratch = torch.empty(backward_scratch_bytes(B, T, H, D), device=dout.device, dtype=torch.uint8)
     backward_into(ctx.saved, ctx.out, ctx.lse, dout, dqkv, scratch, H, ctx.flags)
     return dqkv
+
+
+# ---------------------------------------------------------------------------------------------
+# Linear either side of the attention layer (include/linear_sm100.h); mirrors the reference's
+# linear_forward_cuda_kernel / linear_backward_cuda_kernel (kernels/src/cuda/Linear.cu:37-92).
+# ---------------------------------------------------------------------------------------------
+def linear_forward(x, w, bias=None, planes=None, stream=None):
+    """y[..., N] = x[..., K] @ w[N, K].T + bias.  `planes`: optional uint8 CUDA tensor of
+    saved_bytes(...) bytes that receives y as bf16 hi/lo planes for the attention kernels."""
+    import torch
+
+    K = x.shape[-1]
+    N = w.shape[0]
+    M = x.numel() // K
+    y = torch.empty((*x.shape[:-1], N), device=x.device, dtype=torch.float32)
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().linear_sm100_forward(_ptr(x), _ptr(w), _ptr(bias), _ptr(y), _ptr(planes), M, N, K, s.cuda_stream),
+           "linear_sm100_forward")
+    return y
+
+
+def linear_backward(dy, x, w, dw, db=None, stream=None):
+    """Returns dx = dy @ w; accumulates dy.T @ x into dw and the column sums of dy into db."""
+    import torch
+
+    K = x.shape[-1]
+    N = w.shape[0]
+    M = x.numel() // K
+    dx = torch.empty_like(x)
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().linear_sm100_backward(_ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, s.cuda_stream),
+           "linear_sm100_backward")
+    return dx

@@ -95,6 +95,31 @@ __global__ void wait_limit_selftest_kernel(int *status, unsigned long long limit
 
 }  // namespace
 
+namespace attn {
+
+int encode_tiled(CUtensorMap *map, CUtensorMapDataType dtype, unsigned rank, const void *base, const cuuint64_t *dims,
+                 const cuuint64_t *strides, const cuuint32_t *box, CUtensorMapSwizzle swizzle) {
+    if (!g_encode) {
+        const int rc = attn_sm100_init();
+        if (rc != ATTN_OK) return rc;
+    }
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = g_encode(map, dtype, rank, const_cast<void *>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+int device_status_word(int **status) {
+    DeviceState *ds = nullptr;
+    const int rc = current_device_state(&ds);
+    if (rc != ATTN_OK) return rc;
+    *status = ds->status;
+    return ATTN_OK;
+}
+
+}  // namespace attn
+
 extern "C" {
 
 int attn_sm100_version(void) { return 100; }

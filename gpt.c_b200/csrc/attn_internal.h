@@ -44,4 +44,12 @@ cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
                                  const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s);
 
+// Helpers shared with the Linear kernels (linear_sm100.cu).
+// cuTensorMapEncodeTiled with the given swizzle, no interleave, no L2 promotion, zero fill; the encoder
+// is resolved by attn_sm100_init.  Returns 0 or a cudaError_t.
+int encode_tiled(CUtensorMap *map, CUtensorMapDataType dtype, unsigned rank, const void *base, const cuuint64_t *dims,
+                 const cuuint64_t *strides, const cuuint32_t *box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
+// Status word of the current device (initialises the library on first use).  Returns ATTN_OK or an error.
+int device_status_word(int **status);
+
 }  // namespace attn

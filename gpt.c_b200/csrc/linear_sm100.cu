@@ -1,0 +1,469 @@
+// Linear layer (y = x W^T + b) and its backward for sm_100a: one persistent tcgen05 GEMM kernel
+// with TF32 inputs read straight from the fp32 tensors and fp32 accumulation in tensor memory.
+//
+// Replaces linear_forward_cuda_kernel / linear_backward_cuda_kernel of gpt.c
+// (kernels/src/cuda/Linear.cu:37-92: one cuBLAS SGEMM in TF32 tensor-op math plus a separate
+// bias kernel forward; two SGEMMs plus an atomic bias reduction backward) for the two Linear
+// layers either side of the attention layer (src/self_attention.c:59-61, 78-80).  The forward
+// epilogue adds the bias and can also emit the result as the two bf16 planes (hi, lo) the
+// attention kernels consume, which removes the attention path's own split pass.
+//
+// The three products differ only in which operand dimension is contiguous in memory:
+//     forward  y [M,N]  = x [M,K] . W[N,K]^T        A: x, K-major          B: W,  K-major
+//     dx       dx[M,K]  = dy[M,N] . W[N,K]          A: dy, K-major (over N) B: W,  MN-major
+//     dW       dW[N,K] += dy[M,N]^T . x[M,K]        A: dy, MN-major         B: x,  MN-major  (split over M)
+// (K-major: the contraction index is the contiguous one.)  Tiles are 128 x 128 with contraction
+// blocks of 32 fp32 values (one 128-byte swizzled row), four stages.
+//
+// Warp roles (256 threads, one CTA per SM, grid = number of SMs, tiles handed out round robin):
+//   warp 0      TMA producer
+//   warp 1      MMA issuer (kind::tf32, M128 N128 K8, one elected lane)
+//   warp 2      tensor-memory allocation (2 accumulators of 128 columns: the epilogue of one tile
+//               overlaps the main loop of the next)
+//   warps 4-7   epilogue: accumulator -> registers -> (+bias, bf16 split) -> swizzled staging tile
+//               in shared memory -> bulk tensor store (forward, dx) or bulk tensor reduction (dW)
+// All waits are bounded (see tc05.cuh).
+#include "attn_internal.h"
+#include "tc05.cuh"
+
+#include "../../include/linear_sm100.h"
+
+namespace lin {
+namespace {
+
+using namespace tc05;
+
+constexpr int kBM = 128, kBN = 128, kBK = 32;
+constexpr int kStages = 4;
+constexpr int kTileBytes = 128 * kBK * 4;  // one operand tile of one stage: 16 KiB
+constexpr int kThreads = 256;
+constexpr int kEpiThreads = 128;
+constexpr uint32_t kTmemCols = 256;
+
+struct __align__(1024) Smem {
+    uint8_t a[kStages][kTileBytes];
+    uint8_t b[kStages][kTileBytes];
+    // 64 output columns of a tile on their way out: fp32 columns 0-31, fp32 columns 32-63,
+    // bf16 hi plane (64 columns), bf16 lo plane; each [128 rows x 128 bytes], 128-byte swizzled
+    uint8_t out[4][16384];
+    uint64_t full[kStages], empty[kStages];
+    uint64_t acc_full[2], acc_empty[2];
+    uint64_t out_ready, out_free;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct Problem {
+    int M, N, K;  // C is [M, N]; K is the contraction length
+    int tiles_m, tiles_n, splits, kb_total, kb_per_split, total;
+};
+
+enum Site : int {
+    SITE_EMPTY = 201, SITE_FULL, SITE_ACC_EMPTY, SITE_ACC_FULL, SITE_OUT_READY, SITE_OUT_FREE, SITE_SMEM_ALIGN
+};
+
+// Instruction descriptor for kind::tf32 (A and B formats = 2), fp32 accumulation.
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_tf32_lead(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+
+// Shared-memory descriptor for 32-bit operands read MN-major: layout type 1 (128-byte swizzle with
+// 32-byte atoms); rows of 32 values along M/N, LBO = distance between 32-value blocks, SBO = distance
+// between groups of 4 contraction steps.
+__device__ __forceinline__ uint64_t smem_desc_sw128_base32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
+
+struct Work {
+    int m0, n0, kb0, kb1;
+};
+__device__ __forceinline__ Work decode(const Problem &p, int w) {
+    const int split = w % p.splits;
+    const int t = w / p.splits;
+    const int tn = t % p.tiles_n, tm = t / p.tiles_n;
+    Work r;
+    r.m0 = tm * kBM;
+    r.n0 = tn * kBN;
+    r.kb0 = split * p.kb_per_split;
+    r.kb1 = min(p.kb_total, r.kb0 + p.kb_per_split);
+    return r;
+}
+
+// kEpi 0: C = acc (+ bias), optional bf16 planes; kEpi 1: C += acc (bulk reduction)
+template <bool kAMN, bool kBMN, int kEpi>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_planes,
+                   const float *__restrict__ bias, int has_planes, Problem p, int *status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_SMEM_ALIGN);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    WaitCtx ctx{&sm.abort_flag, status};
+
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(&sm.full[i], 1);
+            mbar_init(&sm.empty[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&sm.acc_full[i], 1);
+            mbar_init(&sm.acc_empty[i], kEpiThreads);
+        }
+        mbar_init(&sm.out_ready, kEpiThreads);
+        mbar_init(&sm.out_free, 1);
+        fence_barrier_init();
+    }
+    if (warp == 2) {
+        tmem_alloc(&sm.tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a);
+            tma_prefetch_desc(&map_b);
+            int it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x) {
+                const Work wk = decode(p, w);
+                for (int kb = wk.kb0; kb < wk.kb1; kb++, it++) {
+                    const int st = it % kStages;
+                    if (it >= kStages && !mbar_wait(&sm.empty[st], ((it / kStages) - 1) & 1, ctx, SITE_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&sm.full[st], 2 * kTileBytes);
+                    // K-major: map {contraction, rows}, one box {32, 128}.  MN-major: map {rows, contraction},
+                    // four boxes {32, 32}: blocks of 32 rows, each [32 contraction steps x 128 bytes].
+                    if (kAMN) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            tma_load_4d(sm.a[st] + i * 4096, &map_a, &sm.full[st], wk.m0 + 32 * i, kb * kBK, 0, 0);
+                    } else {
+                        tma_load_4d(sm.a[st], &map_a, &sm.full[st], kb * kBK, wk.m0, 0, 0);
+                    }
+                    if (kBMN) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            tma_load_4d(sm.b[st] + i * 4096, &map_b, &sm.full[st], wk.n0 + 32 * i, kb * kBK, 0, 0);
+                    } else {
+                        tma_load_4d(sm.b[st], &map_b, &sm.full[st], kb * kBK, wk.n0, 0, 0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        constexpr uint32_t idesc = idesc_tf32(kBM, kBN, kAMN ? 1 : 0, kBMN ? 1 : 0);
+        const uint32_t leader = elect_leader();
+        int it = 0, j = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x, j++) {
+            const Work wk = decode(p, w);
+            const int acc = j & 1;
+            if (j >= 2 && !mbar_wait_warp(&sm.acc_empty[acc], ((j >> 1) - 1) & 1, ctx, SITE_ACC_EMPTY)) break;
+            tc_fence_after_sync();
+            const uint32_t d = tmem + (uint32_t)acc * kBN;
+            for (int kb = wk.kb0; kb < wk.kb1; kb++, it++) {
+                const int st = it % kStages;
+                if (!mbar_wait_warp(&sm.full[st], (it / kStages) & 1, ctx, SITE_FULL)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                // MN-major tiles: 32-row blocks 4096 bytes apart, groups of 4 contraction steps 512 bytes apart
+                const uint64_t ad = kAMN ? smem_desc_sw128_base32(smem_u32(sm.a[st]), 4096, 512)
+                                         : smem_desc_sw128(smem_u32(sm.a[st]), 16, 1024);
+                const uint64_t bd = kBMN ? smem_desc_sw128_base32(smem_u32(sm.b[st]), 4096, 512)
+                                         : smem_desc_sw128(smem_u32(sm.b[st]), 16, 1024);
+#pragma unroll
+                for (int k = 0; k < kBK / 8; k++)
+                    mma_tf32_lead(leader, d, desc_advance(ad, k * (kAMN ? 1024 : 32)),
+                                  desc_advance(bd, k * (kBMN ? 1024 : 32)), idesc, (kb > wk.kb0 || k > 0) ? 1u : 0u);
+                tc_commit_lead(leader, &sm.empty[st]);
+            }
+            if (ok) tc_commit_lead(leader, &sm.acc_full[acc]);
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;
+        const int row = (quarter << 5) | lane;
+        const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
+        int j = 0, chunk_count = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x, j++) {
+            const Work wk = decode(p, w);
+            const int acc = j & 1;
+            if (!mbar_wait_warp(&sm.acc_full[acc], (j >> 1) & 1, ctx, SITE_ACC_FULL)) break;
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < 2; c++, chunk_count++) {
+                const int col0 = wk.n0 + 64 * c;
+                uint32_t r4[4][16];  // 64 columns of this row
+#define R(i) r4[(i) >> 4][(i) & 15]
+#pragma unroll
+                for (int q = 0; q < 4; q++) tmem_ld16(tmem + lane_addr + (uint32_t)acc * kBN + 64 * c + 16 * q, r4[q]);
+                tmem_wait_ld();
+                if (c == 1) {  // the accumulator has been read out: the tensor cores may reuse it
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.acc_empty[acc]);
+                }
+                if (kEpi == 0 && bias != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 16; q++) {
+                        if (col0 + 4 * q < p.N) {  // N is a multiple of 4
+                            const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + col0) + q);
+                            R(4 * q) = __float_as_uint(__uint_as_float(R(4 * q)) + bv.x);
+                            R(4 * q + 1) = __float_as_uint(__uint_as_float(R(4 * q + 1)) + bv.y);
+                            R(4 * q + 2) = __float_as_uint(__uint_as_float(R(4 * q + 2)) + bv.z);
+                            R(4 * q + 3) = __float_as_uint(__uint_as_float(R(4 * q + 3)) + bv.w);
+                        }
+                    }
+                }
+                // the copy engine must have read the previous chunk out of the staging tile
+                if (chunk_count >= 1 && !mbar_wait_warp(&sm.out_free, (chunk_count - 1) & 1, ctx, SITE_OUT_FREE)) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int q = 0; q < 16; q++) {  // fp32: two boxes of 32 columns, 8 chunks of 16 bytes per row
+                    uint8_t *dst = sm.out[q >> 3] + row * 128 + (((q & 7) ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(R(4 * q), R(4 * q + 1), R(4 * q + 2), R(4 * q + 3));
+                }
+                if (kEpi == 0 && has_planes) {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {  // bf16 planes: 64 columns = 8 chunks of 8 values
+                        uint32_t h[4], l[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float f0 = __uint_as_float(R(8 * q + 2 * e)), f1 = __uint_as_float(R(8 * q + 2 * e + 1));
+                            const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                            const __nv_bfloat162 ll = __floats2bfloat162_rn(f0 - __low2float(hh), f1 - __high2float(hh));
+                            h[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                            l[e] = *reinterpret_cast<const uint32_t *>(&ll);
+                        }
+                        const int off = row * 128 + ((q ^ (row & 7)) << 4);
+                        *reinterpret_cast<uint4 *>(sm.out[2] + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4 *>(sm.out[3] + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                    }
+                }
+#undef R
+                fence_proxy_async_smem();
+                mbar_arrive(&sm.out_ready);
+                if (threadIdx.x == 128) {
+                    if (!mbar_wait(&sm.out_ready, chunk_count & 1, ctx, SITE_OUT_READY)) {
+                        ok = false;
+                    } else {
+                        if (kEpi == 0) {
+                            tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                            tma_store_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                            if (has_planes) {
+                                tma_store_3d(sm.out[2], &map_planes, col0, wk.m0, 0);
+                                tma_store_3d(sm.out[3], &map_planes, col0, wk.m0, 1);
+                            }
+                        } else {
+                            tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                            tma_reduce_add_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                        }
+                        bulk_commit();
+                        bulk_wait_read_all();
+                        mbar_arrive(&sm.out_free);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+        }
+    }
+
+    // ------------------------------ tear-down ------------------------------
+    if (sm.abort_flag) __nanosleep(50000);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// db[n] += sum_m dy[m, n]: 32 columns per block column, rows strided over blockIdx.y.
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ db, int M, int N) {
+    __shared__ float part[8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int rl = threadIdx.x >> 5;
+    float acc = 0.f;
+    if (col < N)
+        for (int m = blockIdx.y * 8 + rl; m < M; m += gridDim.y * 8) acc += __ldcs(dy + (size_t)m * N + col);
+    part[rl][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (rl == 0 && col < N) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += part[i][threadIdx.x];
+        atomicAdd(db + col, s);
+    }
+}
+
+// ---- host side ----
+
+// Operand read K-major: matrix [rows, kc] row-major (kc contiguous = contraction).
+int map_k_major(CUtensorMap *map, const float *base, int rows, int kc) {
+    const cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)rows, 1, 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)kc * 4, (cuuint64_t)kc * 4 * (cuuint64_t)rows, (cuuint64_t)kc * 4 * (cuuint64_t)rows};
+    const cuuint32_t box[4] = {32, 128, 1, 1};
+    return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box);
+}
+// Operand read MN-major: matrix [kc, rows] row-major (rows contiguous, kc = contraction), boxes of 32 x 32.
+int map_mn_major(CUtensorMap *map, const float *base, int kc, int rows) {
+    const cuuint64_t dims[4] = {(cuuint64_t)rows, (cuuint64_t)kc, 1, 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)rows * 4, (cuuint64_t)rows * 4 * (cuuint64_t)kc, (cuuint64_t)rows * 4 * (cuuint64_t)kc};
+    const cuuint32_t box[4] = {32, 32, 1, 1};
+    // 32-bit operands read MN-major need the 128-byte swizzle with 32-byte atoms (rows of 128 bytes, the
+    // 32-byte quarter of a row XORed with the row index modulo 4)
+    return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
+int map_out_f32(CUtensorMap *map, const float *base, int rows, int cols) {
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)cols * 4 * (cuuint64_t)rows};
+    const cuuint32_t box[3] = {32, 128, 1};
+    return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box);
+}
+int map_out_planes(CUtensorMap *map, const void *base, int rows, int cols) {
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)attn::plane_bytes((size_t)rows * cols)};
+    const cuuint32_t box[3] = {64, 128, 1};
+    return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box);
+}
+
+Problem make_problem(int M, int N, int K, int splits) {
+    Problem p;
+    p.M = M, p.N = N, p.K = K;
+    p.tiles_m = (M + kBM - 1) / kBM;
+    p.tiles_n = (N + kBN - 1) / kBN;
+    p.kb_total = (K + kBK - 1) / kBK;
+    if (splits < 1) splits = 1;
+    if (splits > p.kb_total) splits = p.kb_total;
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // every split is non-empty
+    p.total = p.tiles_m * p.tiles_n * p.splits;
+    return p;
+}
+
+template <bool kAMN, bool kBMN, int kEpi>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp, const float *bias,
+           int has_planes, const Problem &p, int *status, cudaStream_t s) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    auto kernel = linear_gemm_kernel<kAMN, kBMN, kEpi>;
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+        if (e != cudaSuccess) return (int)e;
+        attr_done[dev] = true;
+    }
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    const int grid = p.total < sms ? p.total : sms;
+    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, has_planes, p, status);
+    return (int)cudaGetLastError();
+}
+
+bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
+
+}  // namespace
+}  // namespace lin
+
+extern "C" {
+
+int linear_sm100_forward(const float *x, const float *w, const float *bias, float *y, void *planes, int M, int N, int K,
+                         void *stream) {
+    using namespace lin;
+    if (!x || !w || !y) return ATTN_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || (long long)M * N > 0x7fffffffLL || (long long)M * K > 0x7fffffffLL) return ATTN_ERR_SHAPE;
+    if (K % 4 != 0 || N % 4 != 0 || (planes && N % 8 != 0)) return ATTN_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (bias && !aligned16(bias)) || (planes && !aligned16(planes)))
+        return ATTN_ERR_ALIGN;
+    int *status = nullptr;
+    int rc = attn::device_status_word(&status);
+    if (rc != ATTN_OK) return rc;
+    CUtensorMap ma, mb, mc, mp;
+    if ((rc = map_k_major(&ma, x, M, K)) != 0) return rc;
+    if ((rc = map_k_major(&mb, w, N, K)) != 0) return rc;
+    if ((rc = map_out_f32(&mc, y, M, N)) != 0) return rc;
+    mp = mc;
+    if (planes && (rc = map_out_planes(&mp, planes, M, N)) != 0) return rc;
+    const Problem p = make_problem(M, N, K, 1);
+    return launch<false, false, 0>(ma, mb, mc, mp, bias, planes ? 1 : 0, p, status, static_cast<cudaStream_t>(stream));
+}
+
+int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, int M, int N,
+                          int K, void *stream) {
+    using namespace lin;
+    if (!dy || !x || !w || !dx || !dw) return ATTN_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || (long long)M * N > 0x7fffffffLL || (long long)M * K > 0x7fffffffLL) return ATTN_ERR_SHAPE;
+    if (K % 32 != 0 || N % 32 != 0) return ATTN_ERR_UNSUPPORTED;
+    if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw)) return ATTN_ERR_ALIGN;
+    int *status = nullptr;
+    int rc = attn::device_status_word(&status);
+    if (rc != ATTN_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CUtensorMap ma, mb, mc;
+    // dx[M,K] = dy[M,N] . w[N,K]: contraction over N
+    if ((rc = map_k_major(&ma, dy, M, N)) != 0) return rc;
+    if ((rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
+    if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
+    rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, 0, make_problem(M, K, N, 1), status, s);
+    if (rc != 0) return rc;
+    // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work
+    if ((rc = map_mn_major(&ma, dy, M, N)) != 0) return rc;
+    if ((rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
+    if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
+    const int tiles = ((N + kBM - 1) / kBM) * ((K + kBN - 1) / kBN);
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int splits = (2 * sms + tiles - 1) / tiles;  // about two work items per SM
+    rc = launch<true, true, 1>(ma, mb, mc, mc, nullptr, 0, make_problem(N, K, M, splits), status, s);
+    if (rc != 0) return rc;
+    if (db) {
+        dim3 grid((unsigned)((N + 31) / 32), (unsigned)(M >= 4096 ? 64 : (M + 63) / 64));
+        bias_grad_kernel<<<grid, 256, 0, s>>>(dy, db, M, N);
+        rc = (int)cudaGetLastError();
+    }
+    return rc;
+}
+
+}  // extern "C"

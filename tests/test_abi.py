@@ -6,13 +6,17 @@ import re
 
 import pytest
 
-HEADER = os.path.join(os.path.dirname(__file__), "..", "include", "attn_sm100.h")
+INCLUDE = os.path.join(os.path.dirname(__file__), "..", "include")
+HEADERS = ["attn_sm100.h", "linear_sm100.h"]
 
 
 def declared_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(attn_sm100_\w+)\s*\(", text)))
+    names = set()
+    for header in HEADERS:
+        text = open(os.path.join(INCLUDE, header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b((?:attn|linear)_sm100_\w+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_declares_something():
@@ -23,7 +27,7 @@ def test_header_declares_something():
 def test_library_exports_every_declared_symbol(pkg):
     handle = pkg.lib()
     for name in declared_functions():
-        assert hasattr(handle, name), f"{name} declared in include/attn_sm100.h but not exported"
+        assert hasattr(handle, name), f"{name} declared under include/ but not exported"
     assert set(pkg.SIGNATURES) == set(declared_functions())
 
 
