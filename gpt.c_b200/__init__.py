@@ -175,14 +175,15 @@ def linear_forward(x, w, bias=None, planes=None, stream=None):
     return y
 
 
-def linear_backward(dy, x, w, dw, db=None, stream=None):
-    """Returns dx = dy @ w; accumulates dy.T @ x into dw and the column sums of dy into db."""
+def linear_backward(dy, x, w, dw, db=None, stream=None, want_dx=True):
+    """Returns dx = dy @ w (None when want_dx is false); accumulates dy.T @ x into dw (skipped when dw is
+    None) and the column sums of dy into db."""
     import torch
 
     K = x.shape[-1]
     N = w.shape[0]
     M = x.numel() // K
-    dx = torch.empty_like(x)
+    dx = torch.empty_like(x) if want_dx else None
     s = torch.cuda.current_stream() if stream is None else stream
     _check(lib().linear_sm100_backward(_ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, s.cuda_stream),
            "linear_sm100_backward")

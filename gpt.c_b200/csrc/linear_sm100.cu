@@ -15,13 +15,14 @@
 // (K-major: the contraction index is the contiguous one.)  Tiles are 128 x 128 with contraction
 // blocks of 32 fp32 values (one 128-byte swizzled row), four stages.
 //
-// Warp roles (256 threads, one CTA per SM, grid = number of SMs, tiles handed out round robin):
+// Warp roles (384 threads, one CTA per SM, grid = number of SMs, tiles handed out round robin):
 //   warp 0      TMA producer
 //   warp 1      MMA issuer (kind::tf32, M128 N128 K8, one elected lane)
 //   warp 2      tensor-memory allocation (2 accumulators of 128 columns: the epilogue of one tile
 //               overlaps the main loop of the next)
-//   warps 4-7   epilogue: accumulator -> registers -> (+bias, bf16 split) -> swizzled staging tile
-//               in shared memory -> bulk tensor store (forward, dx) or bulk tensor reduction (dW)
+//   warps 4-11  epilogue, two warps per tensor-memory lane quarter: accumulator -> registers ->
+//               (+bias, bf16 split) -> swizzled staging tile in shared memory
+//   warp 3      bulk tensor store (forward, dx) or bulk tensor reduction (dW) of each staged chunk
 // All waits are bounded (see tc05.cuh).
 #include "attn_internal.h"
 #include "tc05.cuh"
@@ -33,19 +34,21 @@ namespace {
 
 using namespace tc05;
 
-constexpr int kBM = 128, kBN = 128, kBK = 32;
-constexpr int kStages = 4;
-constexpr int kTileBytes = 128 * kBK * 4;  // one operand tile of one stage: 16 KiB
-constexpr int kThreads = 256;
-constexpr int kEpiThreads = 128;
-constexpr uint32_t kTmemCols = 256;
+constexpr int kBM = 128, kBK = 32;
+constexpr int kATileBytes = kBM * kBK * 4;  // A tile of one stage: 16 KiB
+constexpr int kThreads = 384;
+constexpr int kEpiThreads = 256;
+constexpr int kMaxStages = 6;
 
-struct __align__(1024) Smem {
-    uint8_t a[kStages][kTileBytes];
-    uint8_t b[kStages][kTileBytes];
-    // 64 output columns of a tile on their way out: fp32 columns 0-31, fp32 columns 32-63,
-    // bf16 hi plane (64 columns), bf16 lo plane; each [128 rows x 128 bytes], 128-byte swizzled
-    uint8_t out[4][16384];
+// Tile width kBN (128 or 256 columns) and pipeline depth are chosen per problem: wide tiles halve the
+// shared-memory and L2 traffic per flop, narrow ones fill the SMs better when there are few tiles.
+template <int kBN, int kStages, bool kPlanes>
+struct __align__(1024) SmemT {
+    uint8_t a[kStages][kATileBytes];
+    uint8_t b[kStages][kBN * kBK * 4];
+    // 64 output columns of a tile on their way out: fp32 columns 0-31, fp32 columns 32-63 and, when the
+    // bf16 planes are wanted, hi plane (64 columns), lo plane; each [128 rows x 128 bytes], swizzled
+    uint8_t out[kPlanes ? 4 : 2][16384];
     uint64_t full[kStages], empty[kStages];
     uint64_t acc_full[2], acc_empty[2];
     uint64_t out_ready, out_free;
@@ -55,6 +58,7 @@ struct __align__(1024) Smem {
 
 struct Problem {
     int M, N, K;  // C is [M, N]; K is the contraction length
+    int bn;       // tile width
     int tiles_m, tiles_n, splits, kb_total, kb_per_split, total;
 };
 
@@ -103,19 +107,22 @@ __device__ __forceinline__ Work decode(const Problem &p, int w) {
     const int tn = t % p.tiles_n, tm = t / p.tiles_n;
     Work r;
     r.m0 = tm * kBM;
-    r.n0 = tn * kBN;
+    r.n0 = tn * p.bn;
     r.kb0 = split * p.kb_per_split;
     r.kb1 = min(p.kb_total, r.kb0 + p.kb_per_split);
     return r;
 }
 
 // kEpi 0: C = acc (+ bias), optional bf16 planes; kEpi 1: C += acc (bulk reduction)
-template <bool kAMN, bool kBMN, int kEpi>
+template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_planes,
                    const float *__restrict__ bias, int has_planes, Problem p, int *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    using Smem = SmemT<kBN, kStages, kPlanes>;
+    constexpr uint32_t kTmemCols = 2 * kBN <= 256 ? 256 : 512;  // a power of two that holds two accumulators
+    constexpr int kBTileBytes = kBN * kBK * 4;
     Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_SMEM_ALIGN);
@@ -162,7 +169,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&sm.full[st], 2 * kTileBytes);
+                    mbar_expect_tx(&sm.full[st], kATileBytes + kBTileBytes);
                     // K-major: map {contraction, rows}, one box {32, 128}.  MN-major: map {rows, contraction},
                     // four boxes {32, 32}: blocks of 32 rows, each [32 contraction steps x 128 bytes].
                     if (kAMN) {
@@ -174,10 +181,12 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                     if (kBMN) {
 #pragma unroll
-                        for (int i = 0; i < 4; i++)
+                        for (int i = 0; i < kBN / 32; i++)
                             tma_load_4d(sm.b[st] + i * 4096, &map_b, &sm.full[st], wk.n0 + 32 * i, kb * kBK, 0, 0);
                     } else {
-                        tma_load_4d(sm.b[st], &map_b, &sm.full[st], kb * kBK, wk.n0, 0, 0);
+#pragma unroll
+                        for (int i = 0; i < kBN / 64; i++)  // the B map's box is 64 rows
+                            tma_load_4d(sm.b[st] + i * 8192, &map_b, &sm.full[st], kb * kBK, wk.n0 + 64 * i, 0, 0);
                     }
                 }
             }
@@ -216,7 +225,10 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
     } else if (warp >= 4) {
         // ------------------------------ epilogue ------------------------------
+        // Two warps per tensor-memory lane quarter: each thread owns one row and 32 of the 64 columns
+        // of a chunk.  Warp 3 drives the copy engine.
         const int quarter = warp & 3;
+        const int half = (warp - 4) >> 2;
         const int row = (quarter << 5) | lane;
         const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
         int j = 0, chunk_count = 0;
@@ -227,20 +239,21 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (!mbar_wait_warp(&sm.acc_full[acc], (j >> 1) & 1, ctx, SITE_ACC_FULL)) break;
             tc_fence_after_sync();
 #pragma unroll 1
-            for (int c = 0; c < 2; c++, chunk_count++) {
-                const int col0 = wk.n0 + 64 * c;
-                uint32_t r4[4][16];  // 64 columns of this row
-#define R(i) r4[(i) >> 4][(i) & 15]
+            for (int c = 0; c < kBN / 64; c++, chunk_count++) {
+                const int col0 = wk.n0 + 64 * c + 32 * half;  // first of this thread's 32 columns
+                uint32_t r2[2][16];
+#define R(i) r2[(i) >> 4][(i) & 15]
 #pragma unroll
-                for (int q = 0; q < 4; q++) tmem_ld16(tmem + lane_addr + (uint32_t)acc * kBN + 64 * c + 16 * q, r4[q]);
+                for (int q = 0; q < 2; q++)
+                    tmem_ld16(tmem + lane_addr + (uint32_t)acc * kBN + 64 * c + 32 * half + 16 * q, r2[q]);
                 tmem_wait_ld();
-                if (c == 1) {  // the accumulator has been read out: the tensor cores may reuse it
+                if (c == kBN / 64 - 1) {  // the accumulator has been read out: the tensor cores may reuse it
                     tc_fence_before_sync();
                     mbar_arrive(&sm.acc_empty[acc]);
                 }
                 if (kEpi == 0 && bias != nullptr) {
 #pragma unroll
-                    for (int q = 0; q < 16; q++) {
+                    for (int q = 0; q < 8; q++) {
                         if (col0 + 4 * q < p.N) {  // N is a multiple of 4
                             const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + col0) + q);
                             R(4 * q) = __float_as_uint(__uint_as_float(R(4 * q)) + bv.x);
@@ -250,58 +263,70 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         }
                     }
                 }
+                uint32_t hp[16], lp[16];  // packed bf16 pairs of the two planes
+                if (kEpi == 0 && kPlanes) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) {
+                        const float f0 = __uint_as_float(R(2 * e)), f1 = __uint_as_float(R(2 * e + 1));
+                        const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                        const __nv_bfloat162 ll = __floats2bfloat162_rn(f0 - __low2float(hh), f1 - __high2float(hh));
+                        hp[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                        lp[e] = *reinterpret_cast<const uint32_t *>(&ll);
+                    }
+                }
                 // the copy engine must have read the previous chunk out of the staging tile
                 if (chunk_count >= 1 && !mbar_wait_warp(&sm.out_free, (chunk_count - 1) & 1, ctx, SITE_OUT_FREE)) {
                     ok = false;
                     break;
                 }
 #pragma unroll
-                for (int q = 0; q < 16; q++) {  // fp32: two boxes of 32 columns, 8 chunks of 16 bytes per row
-                    uint8_t *dst = sm.out[q >> 3] + row * 128 + (((q & 7) ^ (row & 7)) << 4);
+                for (int q = 0; q < 8; q++) {  // fp32: this half's box of 32 columns, 8 chunks of 16 bytes per row
+                    uint8_t *dst = sm.out[half] + row * 128 + ((q ^ (row & 7)) << 4);
                     *reinterpret_cast<uint4 *>(dst) = make_uint4(R(4 * q), R(4 * q + 1), R(4 * q + 2), R(4 * q + 3));
                 }
-                if (kEpi == 0 && has_planes) {
+                if (kEpi == 0 && kPlanes) {
 #pragma unroll
-                    for (int q = 0; q < 8; q++) {  // bf16 planes: 64 columns = 8 chunks of 8 values
-                        uint32_t h[4], l[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const float f0 = __uint_as_float(R(8 * q + 2 * e)), f1 = __uint_as_float(R(8 * q + 2 * e + 1));
-                            const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                            const __nv_bfloat162 ll = __floats2bfloat162_rn(f0 - __low2float(hh), f1 - __high2float(hh));
-                            h[e] = *reinterpret_cast<const uint32_t *>(&hh);
-                            l[e] = *reinterpret_cast<const uint32_t *>(&ll);
-                        }
-                        const int off = row * 128 + ((q ^ (row & 7)) << 4);
-                        *reinterpret_cast<uint4 *>(sm.out[2] + off) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4 *>(sm.out[3] + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                    for (int q = 0; q < 4; q++) {  // bf16 planes: this half's 32 columns = 4 chunks of 8 values
+                        const int off = row * 128 + (((4 * half + q) ^ (row & 7)) << 4);
+                        *reinterpret_cast<uint4 *>(sm.out[kPlanes ? 2 : 0] + off) =
+                            make_uint4(hp[4 * q], hp[4 * q + 1], hp[4 * q + 2], hp[4 * q + 3]);
+                        *reinterpret_cast<uint4 *>(sm.out[kPlanes ? 3 : 0] + off) =
+                            make_uint4(lp[4 * q], lp[4 * q + 1], lp[4 * q + 2], lp[4 * q + 3]);
                     }
                 }
 #undef R
                 fence_proxy_async_smem();
                 mbar_arrive(&sm.out_ready);
-                if (threadIdx.x == 128) {
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------ output copies ------------------------------
+        if (lane == 0) {
+            int chunk_count = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x) {
+                const Work wk = decode(p, w);
+                for (int c = 0; c < kBN / 64; c++, chunk_count++) {
+                    const int col0 = wk.n0 + 64 * c;
                     if (!mbar_wait(&sm.out_ready, chunk_count & 1, ctx, SITE_OUT_READY)) {
                         ok = false;
-                    } else {
-                        if (kEpi == 0) {
-                            tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
-                            tma_store_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
-                            if (has_planes) {
-                                tma_store_3d(sm.out[2], &map_planes, col0, wk.m0, 0);
-                                tma_store_3d(sm.out[3], &map_planes, col0, wk.m0, 1);
-                            }
-                        } else {
-                            tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
-                            tma_reduce_add_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
-                        }
-                        bulk_commit();
-                        bulk_wait_read_all();
-                        mbar_arrive(&sm.out_free);
+                        break;
                     }
+                    if (kEpi == 0) {
+                        tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                        tma_store_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                        if (kPlanes) {
+                            tma_store_3d(sm.out[kPlanes ? 2 : 0], &map_planes, col0, wk.m0, 0);
+                            tma_store_3d(sm.out[kPlanes ? 3 : 0], &map_planes, col0, wk.m0, 1);
+                        }
+                    } else {
+                        tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                        tma_reduce_add_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                    }
+                    bulk_commit();
+                    bulk_wait_read_all();
+                    mbar_arrive(&sm.out_free);
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
             }
         }
     }
@@ -316,31 +341,48 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
 }
 
-// db[n] += sum_m dy[m, n]: 32 columns per block column, rows strided over blockIdx.y.
+// db[n] += sum_m dy[m, n].  A block covers 128 columns (one float4 per lane) and every 8th row of its
+// share of the rows; four loads are in flight per thread.  N is a multiple of 4.
 __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ db, int M, int N) {
-    __shared__ float part[8][33];
-    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
-    const int rl = threadIdx.x >> 5;
-    float acc = 0.f;
-    if (col < N)
-        for (int m = blockIdx.y * 8 + rl; m < M; m += gridDim.y * 8) acc += __ldcs(dy + (size_t)m * N + col);
-    part[rl][threadIdx.x & 31] = acc;
+    __shared__ float4 part[8][32];
+    const int lane = threadIdx.x & 31, rl = threadIdx.x >> 5;
+    const int col = blockIdx.x * 128 + 4 * lane;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < N) {
+        const int step = gridDim.y * 8;
+        int m = blockIdx.y * 8 + rl;
+        for (; m + 3 * step < M; m += 4 * step) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)(m + u * step) * N + col));
+#pragma unroll
+            for (int u = 0; u < 4; u++) acc.x += v[u].x, acc.y += v[u].y, acc.z += v[u].z, acc.w += v[u].w;
+        }
+        for (; m < M; m += step) {
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)m * N + col));
+            acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+        }
+    }
+    part[rl][lane] = acc;
     __syncthreads();
     if (rl == 0 && col < N) {
-        float s = 0.f;
+        float4 t = part[0][lane];
 #pragma unroll
-        for (int i = 0; i < 8; i++) s += part[i][threadIdx.x];
-        atomicAdd(db + col, s);
+        for (int i = 1; i < 8; i++) t.x += part[i][lane].x, t.y += part[i][lane].y, t.z += part[i][lane].z, t.w += part[i][lane].w;
+        atomicAdd(db + col, t.x);
+        atomicAdd(db + col + 1, t.y);
+        atomicAdd(db + col + 2, t.z);
+        atomicAdd(db + col + 3, t.w);
     }
 }
 
 // ---- host side ----
 
-// Operand read K-major: matrix [rows, kc] row-major (kc contiguous = contraction).
-int map_k_major(CUtensorMap *map, const float *base, int rows, int kc) {
+// Operand read K-major: matrix [rows, kc] row-major (kc contiguous = contraction); boxes of 32 x box_rows.
+int map_k_major(CUtensorMap *map, const float *base, int rows, int kc, int box_rows) {
     const cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)rows, 1, 1};
     const cuuint64_t strides[3] = {(cuuint64_t)kc * 4, (cuuint64_t)kc * 4 * (cuuint64_t)rows, (cuuint64_t)kc * 4 * (cuuint64_t)rows};
-    const cuuint32_t box[4] = {32, 128, 1, 1};
+    const cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
     return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box);
 }
 // Operand read MN-major: matrix [kc, rows] row-major (rows contiguous, kc = contraction), boxes of 32 x 32.
@@ -366,11 +408,11 @@ int map_out_planes(CUtensorMap *map, const void *base, int rows, int cols) {
     return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box);
 }
 
-Problem make_problem(int M, int N, int K, int splits) {
+Problem make_problem(int M, int N, int K, int bn, int splits) {
     Problem p;
-    p.M = M, p.N = N, p.K = K;
+    p.M = M, p.N = N, p.K = K, p.bn = bn;
     p.tiles_m = (M + kBM - 1) / kBM;
-    p.tiles_n = (N + kBN - 1) / kBN;
+    p.tiles_n = (N + bn - 1) / bn;
     p.kb_total = (K + kBK - 1) / kBK;
     if (splits < 1) splits = 1;
     if (splits > p.kb_total) splits = p.kb_total;
@@ -380,25 +422,64 @@ Problem make_problem(int M, int N, int K, int splits) {
     return p;
 }
 
-template <bool kAMN, bool kBMN, int kEpi>
-int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp, const float *bias,
-           int has_planes, const Problem &p, int *status, cudaStream_t s) {
+int sm_count() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
+
+// Tile width for a [M, N] result: the candidate with the fewest (rounds over the SMs) x (tile width),
+// with a fixed charge per tile that makes narrow tiles pay for their higher operand traffic per flop.
+int pick_bn(int M, int N, int splits, int sms) {
+    const int cand[3] = {256, 192, 128};
+    int best = 128;
+    long long best_cost = -1;
+    for (int i = 0; i < 3; i++) {
+        const int bn = cand[i];
+        if (bn > 128 && N < bn) continue;
+        const long long tiles = (long long)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * splits;
+        const long long rounds = (tiles + sms - 1) / sms;
+        const long long cost = rounds * (bn + 192);  // measured: a 192-wide tile costs ~0.9 of a 256-wide one
+        if (best_cost < 0 || cost < best_cost) best = bn, best_cost = cost;
+    }
+    return best;
+}
+
+template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes>
+int launch_one(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp,
+               const float *bias, const Problem &p, int *status, cudaStream_t s) {
+    using Smem = SmemT<kBN, kStages, kPlanes>;
+    static_assert(sizeof(Smem) <= 227 * 1024, "shared memory of the Linear kernel");
     static bool attr_done[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    auto kernel = linear_gemm_kernel<kAMN, kBMN, kEpi>;
+    auto kernel = linear_gemm_kernel<kAMN, kBMN, kEpi, kBN, kStages, kPlanes>;
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    int sms = 0;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
+    const int sms = sm_count();
     const int grid = p.total < sms ? p.total : sms;
-    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, has_planes, p, status);
+    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, kPlanes ? 1 : 0, p, status);
     return (int)cudaGetLastError();
+}
+
+// Pipeline depth by what fits in 227 KiB next to the output staging tile.
+template <bool kAMN, bool kBMN, int kEpi>
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp, const float *bias,
+           bool planes, const Problem &p, int *status, cudaStream_t s) {
+    if (p.bn == 256) {
+        if (planes) return launch_one<kAMN, kBMN, kEpi, 256, 3, true>(ma, mb, mc, mp, bias, p, status, s);
+        return launch_one<kAMN, kBMN, kEpi, 256, 4, false>(ma, mb, mc, mp, bias, p, status, s);
+    }
+    if (p.bn == 192) {
+        if (planes) return launch_one<kAMN, kBMN, kEpi, 192, 4, true>(ma, mb, mc, mp, bias, p, status, s);
+        return launch_one<kAMN, kBMN, kEpi, 192, 4, false>(ma, mb, mc, mp, bias, p, status, s);
+    }
+    if (planes) return launch_one<kAMN, kBMN, kEpi, 128, 5, true>(ma, mb, mc, mp, bias, p, status, s);
+    return launch_one<kAMN, kBMN, kEpi, 128, 6, false>(ma, mb, mc, mp, bias, p, status, s);
 }
 
 bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
@@ -420,46 +501,51 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     int rc = attn::device_status_word(&status);
     if (rc != ATTN_OK) return rc;
     CUtensorMap ma, mb, mc, mp;
-    if ((rc = map_k_major(&ma, x, M, K)) != 0) return rc;
-    if ((rc = map_k_major(&mb, w, N, K)) != 0) return rc;
+    if ((rc = map_k_major(&ma, x, M, K, 128)) != 0) return rc;
+    if ((rc = map_k_major(&mb, w, N, K, 64)) != 0) return rc;
     if ((rc = map_out_f32(&mc, y, M, N)) != 0) return rc;
     mp = mc;
     if (planes && (rc = map_out_planes(&mp, planes, M, N)) != 0) return rc;
-    const Problem p = make_problem(M, N, K, 1);
-    return launch<false, false, 0>(ma, mb, mc, mp, bias, planes ? 1 : 0, p, status, static_cast<cudaStream_t>(stream));
+    const Problem p = make_problem(M, N, K, pick_bn(M, N, 1, sm_count()), 1);
+    return launch<false, false, 0>(ma, mb, mc, mp, bias, planes != nullptr, p, status, static_cast<cudaStream_t>(stream));
 }
 
 int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, int M, int N,
                           int K, void *stream) {
     using namespace lin;
-    if (!dy || !x || !w || !dx || !dw) return ATTN_ERR_NULL;
+    if (!dy || !w || (!dx && !dw) || (dw && !x)) return ATTN_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || (long long)M * N > 0x7fffffffLL || (long long)M * K > 0x7fffffffLL) return ATTN_ERR_SHAPE;
     if (K % 32 != 0 || N % 32 != 0) return ATTN_ERR_UNSUPPORTED;
-    if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw)) return ATTN_ERR_ALIGN;
+    if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) || !aligned16(db))
+        return ATTN_ERR_ALIGN;
     int *status = nullptr;
     int rc = attn::device_status_word(&status);
     if (rc != ATTN_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     CUtensorMap ma, mb, mc;
-    // dx[M,K] = dy[M,N] . w[N,K]: contraction over N
-    if ((rc = map_k_major(&ma, dy, M, N)) != 0) return rc;
-    if ((rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
-    if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
-    rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, 0, make_problem(M, K, N, 1), status, s);
-    if (rc != 0) return rc;
-    // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work
-    if ((rc = map_mn_major(&ma, dy, M, N)) != 0) return rc;
-    if ((rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
-    if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
-    const int tiles = ((N + kBM - 1) / kBM) * ((K + kBN - 1) / kBN);
-    int sms = 148;
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int splits = (2 * sms + tiles - 1) / tiles;  // about two work items per SM
-    rc = launch<true, true, 1>(ma, mb, mc, mc, nullptr, 0, make_problem(N, K, M, splits), status, s);
-    if (rc != 0) return rc;
+    const int sms = sm_count();
+    if (dx) {
+        // dx[M,K] = dy[M,N] . w[N,K]: contraction over N
+        if ((rc = map_k_major(&ma, dy, M, N, 128)) != 0) return rc;
+        if ((rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
+        if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
+        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, make_problem(M, K, N, pick_bn(M, K, 1, sms), 1), status, s);
+        if (rc != 0) return rc;
+    }
+    if (dw) {
+        // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work
+        if ((rc = map_mn_major(&ma, dy, M, N)) != 0) return rc;
+        if ((rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
+        if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
+        const int bn = K % 256 == 0 ? 256 : (K % 192 == 0 ? 192 : 128);
+        const int tiles = ((N + kBM - 1) / kBM) * ((K + bn - 1) / bn);
+        const int splits = (2 * sms + tiles - 1) / tiles;  // about two work items per SM
+        rc = launch<true, true, 1>(ma, mb, mc, mc, nullptr, false, make_problem(N, K, M, bn, splits), status, s);
+        if (rc != 0) return rc;
+    }
     if (db) {
-        dim3 grid((unsigned)((N + 31) / 32), (unsigned)(M >= 4096 ? 64 : (M + 63) / 64));
+        const int by = M >= 2048 ? 32 : (M + 63) / 64;  // rows per block column: at least 8 per row lane
+        dim3 grid((unsigned)((N + 127) / 128), (unsigned)by);
         bias_grad_kernel<<<grid, 256, 0, s>>>(dy, db, M, N);
         rc = (int)cudaGetLastError();
     }

@@ -17,6 +17,7 @@
 #include <cuda/Alloc.h>
 #include <cuda/Attention.h>
 #include "attn_sm100.h"
+#include "attn_planes.h"
 
 static void attn_check(int rc, const char *what) {
     if (rc != ATTN_OK) {
@@ -32,7 +33,18 @@ void attention_forward_cuda_kernel(const tensor_t *input, const tensor_t *mask, 
     (void)mask;
     const int B = input->shape[0], T = input->shape[1], C = input->shape[2] / 3, D = C / n_heads;
     cudaStream_t stream = get_cuda_stream();
-    attn_check(attn_sm100_forward(input->t, output->t, cache[2]->t, cache[1]->t, cache[0]->t, B, T, n_heads, D, 0,
+    int flags = 0;
+    if (D == 64) {
+        // When the Linear in front of this layer already wrote the bf16 planes of this very tensor, adopt
+        // them as cache[0] (they come from the same allocator) and skip the split pass.
+        void *planes = overlay_planes_take(input->t, attn_sm100_saved_bytes(B, T, n_heads, D));
+        if (planes) {
+            free_cuda(cache[0]->t);
+            cache[0]->t = (float *)planes;
+            flags = ATTN_FLAG_CORE_ONLY;
+        }
+    }
+    attn_check(attn_sm100_forward(input->t, output->t, cache[2]->t, cache[1]->t, cache[0]->t, B, T, n_heads, D, flags,
                                   (void *)stream),
                "attn_sm100_forward");
 }

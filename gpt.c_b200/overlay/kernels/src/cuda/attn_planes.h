@@ -1,0 +1,21 @@
+// Hand-off between the Linear adapter and the attention adapter of the overlay: when a Linear
+// forward looks like the fused QKV projection (out_features == 3 * in_features, head size 64),
+// it also emits its result as the bf16 planes the attention kernels read and offers them here;
+// the attention forward that receives the same tensor takes them and skips its own split pass.
+// One slot only: an offer that nobody takes is released by the next offer.
+#pragma once
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// `planes` was allocated with alloc_cuda and holds `bytes` bytes of planes for the tensor at `y`.
+void overlay_planes_offer(const float *y, void *planes, size_t bytes);
+// Returns the planes offered for `y` when they hold at least `bytes` bytes (ownership passes to the
+// caller, who releases them with free_cuda), else NULL.
+void *overlay_planes_take(const float *y, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif

@@ -42,6 +42,8 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
  * dx[M, K]  = dy[M, N] . w[N, K]           (overwritten, like the reference's beta = 0)
  * dw[N, K] += dy[M, N]^T . x[M, K]         (accumulated, like the reference's beta = 1)
  * db[N]    += column sums of dy            (accumulated; db may be NULL)
+ * dx or dw may be NULL (not both): that product is skipped, e.g. dx for a layer whose input needs no
+ * gradient.
  * Requirements: K % 32 == 0 and N % 32 == 0; else ATTN_ERR_UNSUPPORTED.
  * dw and db are built from fp32 additions whose order is not fixed (split over M): results can differ
  * in the last bits between runs.

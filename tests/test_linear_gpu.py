@@ -100,6 +100,22 @@ def test_linear_backward_vs_cpu(pkg, M, N, K):
     assert np.abs(db.cpu().numpy() - db_ref).max() <= 1e-5 * np.sqrt(M) * 8
 
 
+def test_linear_backward_parts_can_be_skipped(pkg):
+    M, N, K = 512, 768, 768
+    x, w, b, dy = inputs(M, N, K, 31)
+    dyt, xt, wt = (torch.from_numpy(a).cuda() for a in (dy, x, w))
+    dw_full = torch.zeros(N, K, device="cuda")
+    dx_full = pkg.linear_backward(dyt, xt, wt, dw_full, None)
+    # dx only
+    dx_only = pkg.linear_backward(dyt, xt, wt, None, None)
+    assert torch.equal(dx_only, dx_full)
+    # dW only (accumulates on top of what is there)
+    dw_only = torch.zeros(N, K, device="cuda")
+    assert pkg.linear_backward(dyt, xt, wt, dw_only, None, want_dx=False) is None
+    assert pkg.device_status() == 0
+    within(dw_only.cpu().numpy(), dy.astype(np.float64).T @ x.astype(np.float64), dy.T, x)
+
+
 def test_linear_argument_errors(pkg):
     L = pkg.lib()
     assert L.linear_sm100_forward(None, None, None, None, None, 1, 4, 4, None) == -1
