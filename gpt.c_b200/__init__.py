@@ -38,6 +38,8 @@ SIGNATURES = {
     "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
     "linear_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
     "linear_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 3 + [_c.c_void_p]),
+    "layernorm_sm100_forward": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_float] + [_c.c_void_p] * 3 + [_c.c_int] * 2 + [_c.c_void_p]),
+    "layernorm_sm100_backward": (_c.c_int, [_c.c_void_p] * 8 + [_c.c_int] * 2 + [_c.c_void_p]),
 }
 
 _lib = None
@@ -188,3 +190,33 @@ def linear_backward(dy, x, w, dw, db=None, stream=None, want_dx=True):
     _check(lib().linear_sm100_backward(_ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, s.cuda_stream),
            "linear_sm100_backward")
     return dx
+
+
+# ---------------------------------------------------------------------------------------------
+# LayerNorm (include/layernorm_sm100.h); mirrors layer_norm_{forward,backward}_cuda_kernel
+# (kernels/src/cuda/LayerNorm.cu:115-165).
+# ---------------------------------------------------------------------------------------------
+def layernorm_forward(x, w, b=None, eps: float = 1e-5, stream=None):
+    """Returns (y, mean, rstd) for x [..., C]."""
+    import torch
+
+    C = x.shape[-1]
+    rows = x.numel() // C
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+    rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().layernorm_sm100_forward(_ptr(x), _ptr(w), _ptr(b), eps, _ptr(mean), _ptr(rstd), _ptr(y), rows, C,
+                                         s.cuda_stream), "layernorm_sm100_forward")
+    return y, mean, rstd
+
+
+def layernorm_backward(dy, x, mean, rstd, w, dw, db, dx, stream=None) -> None:
+    """Accumulates into dw, db (may be None) and dx, like the reference."""
+    import torch
+
+    C = x.shape[-1]
+    rows = x.numel() // C
+    s = torch.cuda.current_stream() if stream is None else stream
+    _check(lib().layernorm_sm100_backward(_ptr(dy), _ptr(x), _ptr(mean), _ptr(rstd), _ptr(w), _ptr(dw), _ptr(db), _ptr(dx),
+                                          rows, C, s.cuda_stream), "layernorm_sm100_backward")

@@ -1,7 +1,7 @@
 """GPT-2 124M training step through the unchanged train_gpt of gpt.c, with the reference's own CUDA
 attention and with this repository's attention (the overlay build), on synthetic inputs.
 
-    python gpt.c_b200/overlay/run_train_config.py [--steps 12] [--layers 12] [--out result.json]
+    python gpt.c_b200/overlay/run_train_config.py [--steps 12] [--layers 12] [--out result.json] [--prepare DIR]
 
 Needs the two builds made by build_libgpt.py under oracle/_ref/ and a CUDA device.  A synthetic
 checkpoint in the reference's format (train_gpt.c:201-287: 256-int header with magic 20240415,
@@ -82,7 +82,20 @@ if __name__ == "__main__":
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--block", type=int, default=1024)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--prepare", default=None, metavar="DIR",
+                    help="only write ckpt.bin and tokens.bin into DIR and print the train_gpt command lines "
+                         "(e.g. to run one of them under a profiler)")
     a = ap.parse_args()
+    if a.prepare:
+        os.makedirs(a.prepare, exist_ok=True)
+        ckpt, tok = os.path.join(a.prepare, "ckpt.bin"), os.path.join(a.prepare, "tokens.bin")
+        write_checkpoint(ckpt, a.layers, a.heads, a.embd, 50257, a.block, seed=1234)
+        write_tokens(tok, a.steps, a.batch, a.block, 50257, seed=4321)
+        for name, d in BUILDS.items():
+            print(name + ":", os.path.join(d, "train_gpt"), f"--train-data={tok}", "--max-epochs=1", f"--batch-size={a.batch}",
+                  f"--block-size={a.block}", f"--load-checkpoint={ckpt}", "--device=cuda", "--lr=3e-4",
+                  f"--log-dir={os.path.join(a.prepare, 'logs_' + name)}")
+        sys.exit(0)
     missing = [k for k, d in BUILDS.items() if not os.path.exists(os.path.join(d, "train_gpt"))]
     if missing:
         sys.exit(f"missing builds {missing}: run gpt.c_b200/overlay/build_libgpt.py where the reference tree is available")
