@@ -40,6 +40,10 @@ SIGNATURES = {
     "linear_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 3 + [_c.c_void_p]),
     "layernorm_sm100_forward": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_float] + [_c.c_void_p] * 3 + [_c.c_int] * 2 + [_c.c_void_p]),
     "layernorm_sm100_backward": (_c.c_int, [_c.c_void_p] * 8 + [_c.c_int] * 2 + [_c.c_void_p]),
+    "tensor_sm100_fill": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_float, _c.c_void_p]),
+    "tensor_sm100_arange": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
+    "tensor_sm100_copy": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "tensor_sm100_axpy": (_c.c_int, [_c.c_size_t, _c.c_float, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
 }
 
 _lib = None
