@@ -188,7 +188,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int jt = (int)(blockIdx.x / BH);  // key tile; tile 0 has the most work and goes first
     const int bh = (int)(blockIdx.x % BH);
     const int b = bh / H, h = bh % H;
-    const int C = H * kD, C3 = 3 * C;
+    const int C = H * kD;
     const int niter = nt - jt;  // query tiles jt .. nt-1
 
     WaitCtx ctx{&sm.abort_flag, status};
@@ -281,7 +281,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint32_t leader = elect_leader();  // the one lane that issues every MMA and commit of this warp
         int s_slot = 0, s_use = 0, e_slot = 0, e_use = 0;
         for (int t = 0; ok && t < 2 * niter; t++) {
-            const int n = t >> 1, hf = t & 1;
+            const int hf = t & 1;
+            [[maybe_unused]] const int n = t >> 1;  // only the trace build reads it
             if (t >= 2) {
                 ok = mbar_wait_warp(&sm.in_empty[e_slot], e_use & 1, ctx, SITE_IN_EMPTY);
                 if (++e_slot == kSlots) { e_slot = 0; e_use++; }
@@ -460,7 +461,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         BWD_LIFE(1);
         const float2 sc2 = make_float2(scale_log2, scale_log2);
         for (int n = 0; ok && n < niter; n++) {
-            const int it = jt + n;
             const bool diag = (n == 0);
             const int lb = n & 1;
             // row statistics of this query tile (warp 2 stages them up to two tiles ahead)

@@ -38,7 +38,6 @@ constexpr int kBM = 128, kBK = 32;
 constexpr int kATileBytes = kBM * kBK * 4;  // A tile of one stage: 16 KiB
 constexpr int kThreads = 384;
 constexpr int kEpiThreads = 256;
-constexpr int kMaxStages = 6;
 
 // Tile width kBN (128 or 256 columns) and pipeline depth are chosen per problem: wide tiles halve the
 // shared-memory and L2 traffic per flop, narrow ones fill the SMs better when there are few tiles.
@@ -114,11 +113,13 @@ __device__ __forceinline__ Work decode(const Problem &p, int w) {
 }
 
 // kEpi 0: C = acc (+ bias), optional bf16 planes; kEpi 1: C += acc (bulk reduction)
-template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes>
+// kDirect: the result goes out with plain coalesced 4-byte stores instead of the copy engine, for outputs
+// whose row pitch is not a multiple of 16 bytes (the 50257-wide vocabulary projection).
+template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes, bool kDirect = false>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_planes,
-                   const float *__restrict__ bias, int has_planes, Problem p, int *status) {
+                   const float *__restrict__ bias, float *__restrict__ c_direct, Problem p, int *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     using Smem = SmemT<kBN, kStages, kPlanes>;
     constexpr uint32_t kTmemCols = 2 * kBN <= 256 ? 256 : 512;  // a power of two that holds two accumulators
@@ -142,7 +143,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             mbar_init(&sm.acc_empty[i], kEpiThreads);
         }
         mbar_init(&sm.out_ready, kEpiThreads);
-        mbar_init(&sm.out_free, 1);
+        mbar_init(&sm.out_free, kDirect ? kEpiThreads : 1);
         fence_barrier_init();
     }
     if (warp == 2) {
@@ -254,7 +255,12 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (kEpi == 0 && bias != nullptr) {
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
-                        if (col0 + 4 * q < p.N) {  // N is a multiple of 4
+                        if (kDirect) {  // N need not be a multiple of 4: element-wise and guarded
+#pragma unroll
+                            for (int e = 0; e < 4; e++)
+                                if (col0 + 4 * q + e < p.N)
+                                    R(4 * q + e) = __float_as_uint(__uint_as_float(R(4 * q + e)) + __ldg(bias + col0 + 4 * q + e));
+                        } else if (col0 + 4 * q < p.N) {  // N is a multiple of 4
                             const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + col0) + q);
                             R(4 * q) = __float_as_uint(__uint_as_float(R(4 * q)) + bv.x);
                             R(4 * q + 1) = __float_as_uint(__uint_as_float(R(4 * q + 1)) + bv.y);
@@ -295,11 +301,31 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                 }
 #undef R
-                fence_proxy_async_smem();
-                mbar_arrive(&sm.out_ready);
+                if (kDirect) {
+                    // every row of the staged chunk is written by one warp instruction: 32 consecutive floats
+                    mbar_arrive(&sm.out_ready);
+                    if (!mbar_wait_warp(&sm.out_ready, chunk_count & 1, ctx, SITE_OUT_READY)) {
+                        ok = false;
+                        break;
+                    }
+                    const int et = threadIdx.x - 128;  // 0..255
+                    const int cbase = wk.n0 + 64 * c;
+#pragma unroll 4
+                    for (int k = 0; k < (128 * 64) / kEpiThreads; k++) {
+                        const int e = et + kEpiThreads * k;
+                        const int rr = e >> 6, cc = e & 63;
+                        const float v = *reinterpret_cast<const float *>(sm.out[cc >> 5] + rr * 128 +
+                                                                         ((((cc & 31) >> 2) ^ (rr & 7)) << 4) + ((cc & 3) << 2));
+                        if (wk.m0 + rr < p.M && cbase + cc < p.N) c_direct[(size_t)(wk.m0 + rr) * p.N + cbase + cc] = v;
+                    }
+                    mbar_arrive(&sm.out_free);
+                } else {
+                    fence_proxy_async_smem();
+                    mbar_arrive(&sm.out_ready);
+                }
             }
         }
-    } else if (warp == 3) {
+    } else if (warp == 3 && !kDirect) {
         // ------------------------------ output copies ------------------------------
         if (lane == 0) {
             int chunk_count = 0;
@@ -445,16 +471,16 @@ int pick_bn(int M, int N, int splits, int sms) {
     return best;
 }
 
-template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes>
+template <bool kAMN, bool kBMN, int kEpi, int kBN, int kStages, bool kPlanes, bool kDirect = false>
 int launch_one(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp,
-               const float *bias, const Problem &p, int *status, cudaStream_t s) {
+               const float *bias, const Problem &p, int *status, cudaStream_t s, float *c_direct = nullptr) {
     using Smem = SmemT<kBN, kStages, kPlanes>;
     static_assert(sizeof(Smem) <= 227 * 1024, "shared memory of the Linear kernel");
     static bool attr_done[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    auto kernel = linear_gemm_kernel<kAMN, kBMN, kEpi, kBN, kStages, kPlanes>;
+    auto kernel = linear_gemm_kernel<kAMN, kBMN, kEpi, kBN, kStages, kPlanes, kDirect>;
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
         if (e != cudaSuccess) return (int)e;
@@ -462,7 +488,7 @@ int launch_one(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &
     }
     const int sms = sm_count();
     const int grid = p.total < sms ? p.total : sms;
-    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, kPlanes ? 1 : 0, p, status);
+    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, c_direct, p, status);
     return (int)cudaGetLastError();
 }
 
@@ -494,8 +520,10 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     using namespace lin;
     if (!x || !w || !y) return ATTN_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || (long long)M * N > 0x7fffffffLL || (long long)M * K > 0x7fffffffLL) return ATTN_ERR_SHAPE;
-    if (K % 4 != 0 || N % 4 != 0 || (planes && N % 8 != 0)) return ATTN_ERR_UNSUPPORTED;
-    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (bias && !aligned16(bias)) || (planes && !aligned16(planes)))
+    const bool direct = N % 4 != 0;  // y's rows are not 16-byte aligned: no copy engine for the output
+    if (K % 4 != 0 || (planes && N % 8 != 0)) return ATTN_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(w) || (!direct && (!aligned16(y) || (bias && !aligned16(bias)))) ||
+        (planes && !aligned16(planes)))
         return ATTN_ERR_ALIGN;
     int *status = nullptr;
     int rc = attn::device_status_word(&status);
@@ -503,6 +531,11 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     CUtensorMap ma, mb, mc, mp;
     if ((rc = map_k_major(&ma, x, M, K, 128)) != 0) return rc;
     if ((rc = map_k_major(&mb, w, N, K, 64)) != 0) return rc;
+    if (direct) {
+        const Problem pd = make_problem(M, N, K, 256, 1);
+        return launch_one<false, false, 0, 256, 4, false, true>(ma, mb, ma, ma, bias, pd, status,
+                                                                static_cast<cudaStream_t>(stream), y);
+    }
     if ((rc = map_out_f32(&mc, y, M, N)) != 0) return rc;
     mp = mc;
     if (planes && (rc = map_out_planes(&mp, planes, M, N)) != 0) return rc;

@@ -3,8 +3,8 @@
 // Drop-in for kernels/src/cuda/Linear.cu of gpt.c: exports linear_forward_cuda_kernel and
 // linear_backward_cuda_kernel with the signatures of kernels/src/cuda/Linear.h:9-18, runs on the
 // reference runtime's stream and prints and exits on error like every CUDA entry of the reference.
-// Shapes the tensor-core kernels do not take (feature counts that are not multiples of 32, e.g. the
-// vocabulary projection) go through the reference runtime's own SGEMM wrapper (sgemm_cuda,
+// Shapes the tensor-core kernels do not take (backward with feature counts that are not multiples of 32,
+// e.g. the vocabulary projection) go through the reference runtime's own SGEMM wrapper (sgemm_cuda,
 // kernels/src/cuda/Tensor.h:24-29) with two small bias kernels below.
 #include <stdio.h>
 #include <stdlib.h>
@@ -58,7 +58,7 @@ __global__ void overlay_bias_grad_kernel(const float *dy, float *db, int rows, i
     atomicAdd(db + col, acc);
 }
 
-static bool fast_forward_ok(int N, int K) { return N % 4 == 0 && K % 4 == 0; }
+static bool fast_forward_ok(int N, int K) { (void)N; return K % 4 == 0; }
 static bool fast_backward_ok(int N, int K) { return N % 32 == 0 && K % 32 == 0; }
 
 extern "C" {

@@ -33,7 +33,9 @@ extern "C" {
  *           lo = bf16(y - hi)), laid out exactly like the `saved` buffer of attn_sm100_forward
  *           (attn_sm100_saved_bytes(B, T, H, D) bytes with 3*H*D = N): the attention layer can then be
  *           called with ATTN_FLAG_CORE_ONLY and skip its own split pass.  No counterpart in the reference.
- * Requirements: K % 4 == 0, N % 4 == 0 (N % 8 == 0 with planes); else ATTN_ERR_UNSUPPORTED.
+ * Requirements: K % 4 == 0 (N % 8 == 0 with planes); else ATTN_ERR_UNSUPPORTED.  When N is not a multiple
+ * of 4 (gpt.c's vocabulary projection, N = 50257) the rows of y are not 16-byte aligned: the result is
+ * then written with plain coalesced stores instead of the copy engine, and y and bias need no alignment.
  */
 int linear_sm100_forward(const float *x, const float *w, const float *bias, float *y, void *planes, int M, int N, int K,
                          void *stream);

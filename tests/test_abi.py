@@ -7,7 +7,7 @@ import re
 import pytest
 
 INCLUDE = os.path.join(os.path.dirname(__file__), "..", "include")
-HEADERS = ["attn_sm100.h", "linear_sm100.h", "layernorm_sm100.h", "tensor_sm100.h", "xent_sm100.h"]
+HEADERS = ["attn_sm100.h", "linear_sm100.h", "layernorm_sm100.h", "tensor_sm100.h", "xent_sm100.h", "adamw_sm100.h"]
 
 
 def declared_functions():
@@ -15,7 +15,7 @@ def declared_functions():
     for header in HEADERS:
         text = open(os.path.join(INCLUDE, header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names |= set(re.findall(r"\b((?:attn|linear|layernorm|tensor|xent)_sm100_\w+)\s*\(", text))
+        names |= set(re.findall(r"\b((?:attn|linear|layernorm|tensor|xent|adamw)_sm100_\w+)\s*\(", text))
     return sorted(names)
 
 

@@ -22,6 +22,8 @@ SHAPES = [
     (300, 2304, 768),              # ragged M (tail tile)
     (256, 96, 64),                 # N, K below one tile
     (1000, 3072, 768),             # MLP up-projection shape
+    (260, 50257, 768),             # vocabulary projection: rows of y not 16-byte aligned, plain stores
+    (130, 1001, 64),               # the same path with a ragged last tile in every direction
 ]
 
 
@@ -123,4 +125,5 @@ def test_linear_argument_errors(pkg):
     p = t.data_ptr()
     assert L.linear_sm100_forward(p, p, None, p, None, 0, 4, 4, None) == -2
     assert L.linear_sm100_forward(p, p, None, p, None, 4, 4, 6, None) == -3
+    assert L.linear_sm100_forward(p, p, None, p, p, 4, 12, 8, None) == -3  # planes need N % 8 == 0
     assert L.linear_sm100_backward(p, p, p, p, p, None, 4, 48, 32, None) == -3
