@@ -37,7 +37,8 @@ SIGNATURES = {
     "attn_sm100_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
     "linear_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
-    "linear_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 3 + [_c.c_void_p]),
+    "linear_sm100_backward_scratch_bytes": (_c.c_size_t, [_c.c_int] * 3),
+    "linear_sm100_backward": (_c.c_int, [_c.c_void_p] * 7 + [_c.c_int] * 3 + [_c.c_void_p]),
     "layernorm_sm100_forward": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_float] + [_c.c_void_p] * 3 + [_c.c_int] * 2 + [_c.c_void_p]),
     "layernorm_sm100_backward": (_c.c_int, [_c.c_void_p] * 8 + [_c.c_int] * 2 + [_c.c_void_p]),
     "tensor_sm100_fill": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_float, _c.c_void_p]),
@@ -194,8 +195,10 @@ def linear_backward(dy, x, w, dw, db=None, stream=None, want_dx=True):
     M = x.numel() // K
     dx = torch.empty_like(x) if want_dx else None
     s = torch.cuda.current_stream() if stream is None else stream
-    _check(lib().linear_sm100_backward(_ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, s.cuda_stream),
-           "linear_sm100_backward")
+    nbytes = lib().linear_sm100_backward_scratch_bytes(M, N, K)
+    scratch = torch.empty(nbytes, device=x.device, dtype=torch.uint8) if nbytes else None
+    _check(lib().linear_sm100_backward(_ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), _ptr(scratch), M, N, K,
+                                       s.cuda_stream), "linear_sm100_backward")
     return dx
 
 

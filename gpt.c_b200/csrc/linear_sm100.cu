@@ -369,7 +369,8 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
 // db[n] += sum_m dy[m, n].  A block covers 128 columns (one float4 per lane) and every 8th row of its
 // share of the rows; four loads are in flight per thread.  N is a multiple of 4.
-__global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ db, int M, int N) {
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ db, int M, int N,
+                                                        int pitch) {
     __shared__ float4 part[8][32];
     const int lane = threadIdx.x & 31, rl = threadIdx.x >> 5;
     const int col = blockIdx.x * 128 + 4 * lane;
@@ -380,12 +381,12 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict_
         for (; m + 3 * step < M; m += 4 * step) {
             float4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) v[u] = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)(m + u * step) * N + col));
+            for (int u = 0; u < 4; u++) v[u] = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)(m + u * step) * pitch + col));
 #pragma unroll
             for (int u = 0; u < 4; u++) acc.x += v[u].x, acc.y += v[u].y, acc.z += v[u].z, acc.w += v[u].w;
         }
         for (; m < M; m += step) {
-            const float4 v = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)m * N + col));
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(dy + (size_t)m * pitch + col));
             acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
         }
     }
@@ -396,9 +397,21 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict_
 #pragma unroll
         for (int i = 1; i < 8; i++) t.x += part[i][lane].x, t.y += part[i][lane].y, t.z += part[i][lane].z, t.w += part[i][lane].w;
         atomicAdd(db + col, t.x);
-        atomicAdd(db + col + 1, t.y);
-        atomicAdd(db + col + 2, t.z);
-        atomicAdd(db + col + 3, t.w);
+        if (col + 1 < N) atomicAdd(db + col + 1, t.y);
+        if (col + 2 < N) atomicAdd(db + col + 2, t.z);
+        if (col + 3 < N) atomicAdd(db + col + 3, t.w);
+    }
+}
+
+// dst[M, Np] = src[M, N] with zero columns N..Np-1: a copy of dy whose rows start on 16-byte boundaries, for
+// outputs of layers whose feature count is not a multiple of 4 (the vocabulary projection).
+__global__ void __launch_bounds__(256) pad_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, int M, int N,
+                                                       int Np) {
+    const size_t total = (size_t)M * Np, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t m = i / Np;
+        const int j = (int)(i - m * Np);
+        dst[i] = j < N ? __ldcs(src + m * N + j) : 0.f;
     }
 }
 
@@ -543,31 +556,50 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     return launch<false, false, 0>(ma, mb, mc, mp, bias, planes != nullptr, p, status, static_cast<cudaStream_t>(stream));
 }
 
-int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, int M, int N,
-                          int K, void *stream) {
+size_t linear_sm100_backward_scratch_bytes(int M, int N, int K) {
+    (void)K;
+    if (M <= 0 || N <= 0 || N % 32 == 0) return 0;
+    const size_t np = ((size_t)N + 31) / 32 * 32;
+    return (size_t)M * np * sizeof(float);
+}
+
+int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, void *scratch,
+                          int M, int N, int K, void *stream) {
     using namespace lin;
     if (!dy || !w || (!dx && !dw) || (dw && !x)) return ATTN_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || (long long)M * N > 0x7fffffffLL || (long long)M * K > 0x7fffffffLL) return ATTN_ERR_SHAPE;
-    if (K % 32 != 0 || N % 32 != 0) return ATTN_ERR_UNSUPPORTED;
-    if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) || !aligned16(db))
+    if (K % 32 != 0) return ATTN_ERR_UNSUPPORTED;
+    const bool padded = N % 32 != 0;  // dy's rows cannot be tiles of the copy engine as they are: work on a padded copy
+    const int np = (N + 31) / 32 * 32;
+    if ((long long)M * np > 0x7fffffffLL) return ATTN_ERR_SHAPE;
+    if (padded && !scratch) return ATTN_ERR_NULL;
+    if ((!padded && !aligned16(dy)) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) ||
+        (!padded && !aligned16(db)) || !aligned16(scratch))
         return ATTN_ERR_ALIGN;
     int *status = nullptr;
     int rc = attn::device_status_word(&status);
     if (rc != ATTN_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    CUtensorMap ma, mb, mc;
     const int sms = sm_count();
+    const float *g = dy;  // [M, np] from here on
+    if (padded) {
+        pad_rows_kernel<<<sms * 16, 256, 0, s>>>(static_cast<float *>(scratch), dy, M, N, np);
+        if ((rc = (int)cudaGetLastError()) != 0) return rc;
+        g = static_cast<const float *>(scratch);
+    }
+    CUtensorMap ma, mb, mc;
     if (dx) {
-        // dx[M,K] = dy[M,N] . w[N,K]: contraction over N
-        if ((rc = map_k_major(&ma, dy, M, N, 128)) != 0) return rc;
+        // dx[M,K] = dy[M,N] . w[N,K]: contraction over N (rows of w past N read as zeros)
+        if ((rc = map_k_major(&ma, g, M, np, 128)) != 0) return rc;
         if ((rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
         if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
-        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, make_problem(M, K, N, pick_bn(M, K, 1, sms), 1), status, s);
+        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, make_problem(M, K, np, pick_bn(M, K, 1, sms), 1), status, s);
         if (rc != 0) return rc;
     }
     if (dw) {
-        // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work
-        if ((rc = map_mn_major(&ma, dy, M, N)) != 0) return rc;
+        // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work (rows of the
+        // result past N are dropped by the copy engine)
+        if ((rc = map_mn_major(&ma, g, M, np)) != 0) return rc;
         if ((rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
         if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
         const int bn = K % 256 == 0 ? 256 : (K % 192 == 0 ? 192 : 128);
@@ -579,7 +611,7 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     if (db) {
         const int by = M >= 2048 ? 32 : (M + 63) / 64;  // rows per block column: at least 8 per row lane
         dim3 grid((unsigned)((N + 127) / 128), (unsigned)by);
-        bias_grad_kernel<<<grid, 256, 0, s>>>(dy, db, M, N);
+        bias_grad_kernel<<<grid, 256, 0, s>>>(g, db, M, N, np);
         rc = (int)cudaGetLastError();
     }
     return rc;

@@ -3,9 +3,9 @@
 // Drop-in for kernels/src/cuda/Linear.cu of gpt.c: exports linear_forward_cuda_kernel and
 // linear_backward_cuda_kernel with the signatures of kernels/src/cuda/Linear.h:9-18, runs on the
 // reference runtime's stream and prints and exits on error like every CUDA entry of the reference.
-// Shapes the tensor-core kernels do not take (backward with feature counts that are not multiples of 32,
-// e.g. the vocabulary projection) go through the reference runtime's own SGEMM wrapper (sgemm_cuda,
-// kernels/src/cuda/Tensor.h:24-29) with two small bias kernels below.
+// Shapes the tensor-core kernels do not take (in_features not a multiple of 4 forward, of 32 backward) go
+// through the reference runtime's own SGEMM wrapper (sgemm_cuda, kernels/src/cuda/Tensor.h:24-29) with two
+// small bias kernels below.
 #include <stdio.h>
 #include <stdlib.h>
 #include <cuda/cuda_common.h>
@@ -59,7 +59,7 @@ __global__ void overlay_bias_grad_kernel(const float *dy, float *db, int rows, i
 }
 
 static bool fast_forward_ok(int N, int K) { (void)N; return K % 4 == 0; }
-static bool fast_backward_ok(int N, int K) { return N % 32 == 0 && K % 32 == 0; }
+static bool fast_backward_ok(int N, int K) { (void)N; return K % 32 == 0; }
 
 extern "C" {
 
@@ -92,9 +92,12 @@ void linear_backward_cuda_kernel(const tensor_t *global_grad, const tensor_t *ca
     const int M = global_grad->shape[0] * global_grad->shape[1];
     cudaStream_t stream = get_cuda_stream();
     if (fast_backward_ok(N, K)) {
-        lin_check(linear_sm100_backward(global_grad->t, cache->t, W->t, dout->t, dW->t, db ? db->t : NULL, M, N, K,
+        const size_t scratch_bytes = linear_sm100_backward_scratch_bytes(M, N, K);
+        void *scratch = scratch_bytes ? alloc_cuda(scratch_bytes) : NULL;
+        lin_check(linear_sm100_backward(global_grad->t, cache->t, W->t, dout->t, dW->t, db ? db->t : NULL, scratch, M, N, K,
                                         (void *)stream),
                   "linear_sm100_backward");
+        free_cuda(scratch);  // stream ordered
         return;
     }
     sgemm_cuda(0, 0, M, K, N, 1.0f, global_grad, 0, N, W, 0, K, 0.0f, dout, 0, K);

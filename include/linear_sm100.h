@@ -41,17 +41,24 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
                          void *stream);
 
 /*
+ * Bytes of device scratch linear_sm100_backward needs: 0 when N is a multiple of 32, else room for a copy of
+ * dy whose rows are padded to the next multiple of 32 columns (the vocabulary projection, N = 50257: its rows
+ * start on 4-byte boundaries only, which the copy engine cannot tile).
+ */
+size_t linear_sm100_backward_scratch_bytes(int M, int N, int K);
+
+/*
  * dx[M, K]  = dy[M, N] . w[N, K]           (overwritten, like the reference's beta = 0)
  * dw[N, K] += dy[M, N]^T . x[M, K]         (accumulated, like the reference's beta = 1)
  * db[N]    += column sums of dy            (accumulated; db may be NULL)
  * dx or dw may be NULL (not both): that product is skipped, e.g. dx for a layer whose input needs no
- * gradient.
- * Requirements: K % 32 == 0 and N % 32 == 0; else ATTN_ERR_UNSUPPORTED.
+ * gradient.  scratch: linear_sm100_backward_scratch_bytes(M, N, K) bytes, 16-byte aligned (NULL when 0).
+ * Requirements: K % 32 == 0; else ATTN_ERR_UNSUPPORTED.
  * dw and db are built from fp32 additions whose order is not fixed (split over M): results can differ
  * in the last bits between runs.
  */
-int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, int M, int N,
-                          int K, void *stream);
+int linear_sm100_backward(const float *dy, const float *x, const float *w, float *dx, float *dw, float *db, void *scratch,
+                          int M, int N, int K, void *stream);
 
 #ifdef __cplusplus
 }

@@ -84,7 +84,7 @@ def test_linear_forward_planes_feed_attention(pkg, oracle):
     assert np.abs(out_a.cpu().numpy() - ref).max() < 2e-3
 
 
-@pytest.mark.parametrize("M,N,K", [s for s in SHAPES if s[1] % 32 == 0 and s[2] % 32 == 0])
+@pytest.mark.parametrize("M,N,K", [s for s in SHAPES if s[2] % 32 == 0])
 def test_linear_backward_vs_cpu(pkg, M, N, K):
     x, w, b, dy = inputs(M, N, K, 23)
     rng = np.random.default_rng(99)
@@ -126,4 +126,7 @@ def test_linear_argument_errors(pkg):
     assert L.linear_sm100_forward(p, p, None, p, None, 0, 4, 4, None) == -2
     assert L.linear_sm100_forward(p, p, None, p, None, 4, 4, 6, None) == -3
     assert L.linear_sm100_forward(p, p, None, p, p, 4, 12, 8, None) == -3  # planes need N % 8 == 0
-    assert L.linear_sm100_backward(p, p, p, p, p, None, 4, 48, 32, None) == -3
+    assert L.linear_sm100_backward(p, p, p, p, p, None, None, 4, 32, 48, None) == -3  # K % 32
+    assert L.linear_sm100_backward(p, p, p, p, p, None, None, 4, 50, 32, None) == -1  # scratch needed, none given
+    assert L.linear_sm100_backward_scratch_bytes(260, 50257, 768) == 260 * 50272 * 4
+    assert L.linear_sm100_backward_scratch_bytes(260, 2304, 768) == 0
