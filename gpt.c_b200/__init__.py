@@ -45,6 +45,8 @@ SIGNATURES = {
     "tensor_sm100_arange": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int, _c.c_void_p]),
     "tensor_sm100_copy": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "tensor_sm100_axpy": (_c.c_int, [_c.c_size_t, _c.c_float, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "tensor_sm100_gelu_forward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "tensor_sm100_gelu_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "xent_sm100_forward": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 2 + [_c.c_void_p]),
     "xent_sm100_backward": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 2 + [_c.c_void_p]),
     "adamw_sm100_step": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] + [_c.c_float] * 5 + [_c.c_int, _c.c_void_p]),

@@ -3,7 +3,8 @@
 // busy).  They replace the one-element-per-thread kernels of gpt.c's kernels/src/cuda/Tensor.cu
 // (:8-28, launched from zeros/ones/fill/arange/copy_tensor_data_cuda :79-130) and its cublasSaxpy
 // wrapper (:132-141) for the contiguous case: the residual adds and copies of every block
-// (src/block.c:69-86, 108-126) and the zero-fills in front of every accumulating backward kernel.
+// (src/block.c:69-86, 108-126) and the zero-fills in front of every accumulating backward kernel; and the
+// tanh-approximated GELU of the MLP (kernels/src/cuda/GeLU.cu), forward and backward.
 // All of them are pure HBM traffic; the bound is the copy bandwidth.
 #include "attn_internal.h"
 
@@ -79,6 +80,54 @@ __global__ void __launch_bounds__(kThreads) axpy_kernel(size_t n, float alpha, c
     }
 }
 
+// tanh-approximated GELU, the reference's formulas (kernels/src/cuda/GeLU.cu:5-38) term for term
+__device__ __forceinline__ float gelu_fwd(float x) {
+    const float kBeta = 0.7978845608028654f;  // sqrt(2 / pi)
+    const float cube = 0.044715f * x * x * x;
+    return 0.5f * x * (1.0f + tanhf(kBeta * (x + cube)));
+}
+__device__ __forceinline__ float gelu_bwd(float g, float x) {
+    const float kBeta = 0.7978845608028654f;
+    const float x_sq = x * x, x_cube = x_sq * x;
+    const float t = tanhf(kBeta * (x + 0.044715f * x_cube));
+    const float left = 0.5f * x, right = 1.0f + t;
+    const float right_derivative = left * (1.0f - t * t) * (kBeta * (1.0f + 3.0f * 0.044715f * x_sq));
+    return g * (0.5f * right + right_derivative);
+}
+
+template <bool kVec>
+__global__ void __launch_bounds__(kThreads) gelu_forward_kernel(const float *__restrict__ x, float *__restrict__ y, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (kVec) {
+        const size_t n4 = n / 4;
+        for (size_t i = tid; i < n4; i += stride) {
+            const float4 a = __ldcs(reinterpret_cast<const float4 *>(x) + i);
+            reinterpret_cast<float4 *>(y)[i] = make_float4(gelu_fwd(a.x), gelu_fwd(a.y), gelu_fwd(a.z), gelu_fwd(a.w));
+        }
+        for (size_t j = n4 * 4 + tid; j < n; j += stride) y[j] = gelu_fwd(x[j]);
+    } else {
+        for (size_t i = tid; i < n; i += stride) y[i] = gelu_fwd(x[i]);
+    }
+}
+
+template <bool kVec>
+__global__ void __launch_bounds__(kThreads) gelu_backward_kernel(const float *__restrict__ g, const float *__restrict__ x,
+                                                                 float *__restrict__ dx, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (kVec) {
+        const size_t n4 = n / 4;
+        for (size_t i = tid; i < n4; i += stride) {
+            const float4 a = __ldcs(reinterpret_cast<const float4 *>(x) + i);
+            const float4 b = __ldcs(reinterpret_cast<const float4 *>(g) + i);
+            reinterpret_cast<float4 *>(dx)[i] =
+                make_float4(gelu_bwd(b.x, a.x), gelu_bwd(b.y, a.y), gelu_bwd(b.z, a.z), gelu_bwd(b.w, a.w));
+        }
+        for (size_t j = n4 * 4 + tid; j < n; j += stride) dx[j] = gelu_bwd(g[j], x[j]);
+    } else {
+        for (size_t i = tid; i < n; i += stride) dx[i] = gelu_bwd(g[i], x[i]);
+    }
+}
+
 }  // namespace
 }  // namespace tens
 
@@ -120,6 +169,26 @@ int tensor_sm100_axpy(size_t n, float alpha, const float *x, float *y, void *str
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (aligned16(x) && aligned16(y)) axpy_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(n, alpha, x, y);
     else axpy_kernel<false><<<grid_for(n), kThreads, 0, s>>>(n, alpha, x, y);
+    return (int)cudaGetLastError();
+}
+
+int tensor_sm100_gelu_forward(const float *x, float *y, size_t n, void *stream) {
+    using namespace tens;
+    if (n == 0) return ATTN_OK;
+    if (!x || !y) return ATTN_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (aligned16(x) && aligned16(y)) gelu_forward_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(x, y, n);
+    else gelu_forward_kernel<false><<<grid_for(n), kThreads, 0, s>>>(x, y, n);
+    return (int)cudaGetLastError();
+}
+
+int tensor_sm100_gelu_backward(const float *g, const float *x, float *dx, size_t n, void *stream) {
+    using namespace tens;
+    if (n == 0) return ATTN_OK;
+    if (!g || !x || !dx) return ATTN_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (aligned16(g) && aligned16(x) && aligned16(dx)) gelu_backward_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(g, x, dx, n);
+    else gelu_backward_kernel<false><<<grid_for(n), kThreads, 0, s>>>(g, x, dx, n);
     return (int)cudaGetLastError();
 }
 

@@ -5,7 +5,7 @@ written under ``oracle/_ref/`` (git-ignored, reference-derived):
 
   oracle/_ref/gptc_overlay/    libgpt.so = reference sources, with src/attention.c,
                                kernels/src/core/Attention.c and kernels/src/cuda/{Attention,Linear,
-                               LayerNorm,Tensor,CrossEntropyLoss,AdamW,Alloc}.cu taken from gpt.c_b200/overlay/, linked
+                               LayerNorm,Tensor,GeLU,CrossEntropyLoss,AdamW,Alloc}.cu taken from gpt.c_b200/overlay/, linked
                                against libattn_sm100.so;
                                plus train_gpt, infer_gpt and layer_driver
   oracle/_ref/gptc_reference/  the same executables from the unmodified reference (its cuBLAS + SIMT
@@ -30,7 +30,7 @@ from oracle.build import find_openblas  # noqa: E402
 ATTN_LIB_DIR = os.path.join(ROOT, "gpt.c_b200", "lib")
 REPLACED = {"src/attention.c", "kernels/src/core/Attention.c", "kernels/src/cuda/Attention.cu",
             "kernels/src/cuda/Linear.cu", "kernels/src/cuda/Alloc.cu", "kernels/src/cuda/LayerNorm.cu", "kernels/src/cuda/Tensor.cu",
-            "kernels/src/cuda/CrossEntropyLoss.cu", "kernels/src/cuda/AdamW.cu"}
+            "kernels/src/cuda/CrossEntropyLoss.cu", "kernels/src/cuda/AdamW.cu", "kernels/src/cuda/GeLU.cu"}
 
 
 def run(cmd):
@@ -59,7 +59,7 @@ def build(ref: str, out_dir: str, overlay: bool) -> str:
         c_srcs = [s for s in c_srcs if os.path.relpath(s, ref) not in REPLACED]
         cu_srcs = [s for s in cu_srcs if os.path.relpath(s, ref) not in REPLACED]
         c_srcs += [os.path.join(HERE, "src/attention.c"), os.path.join(HERE, "kernels/src/core/Attention.c")]
-        cu_srcs += [os.path.join(HERE, "kernels/src/cuda", f) for f in ("Attention.cu", "Linear.cu", "Alloc.cu", "LayerNorm.cu", "Tensor.cu", "CrossEntropyLoss.cu", "AdamW.cu")]
+        cu_srcs += [os.path.join(HERE, "kernels/src/cuda", f) for f in ("Attention.cu", "Linear.cu", "Alloc.cu", "LayerNorm.cu", "Tensor.cu", "CrossEntropyLoss.cu", "AdamW.cu", "GeLU.cu")]
         inc += ["-I", os.path.join(HERE, "kernels/src/cuda")]
 
     jobs = []

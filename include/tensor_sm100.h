@@ -11,6 +11,7 @@
  *   tensor_sm100_arange   arange_tensor_data_cuda            kernels/src/cuda/Tensor.cu:109-117 (kernel :15-20)
  *   tensor_sm100_copy     copy_tensor_data_cuda              kernels/src/cuda/Tensor.cu:119-130 (kernel :22-27)
  *   tensor_sm100_axpy     saxpy_cuda with unit strides       kernels/src/cuda/Tensor.cu:132-141 (cublasSaxpy)
+ *   tensor_sm100_gelu_forward / _backward   gelu_forward/backward_cuda_kernel   kernels/src/cuda/GeLU.cu:40-64 (kernels :5-38)
  */
 #ifndef TENSOR_SM100_H
 #define TENSOR_SM100_H
@@ -29,6 +30,10 @@ int tensor_sm100_arange(float *p, size_t n, int start, int step, void *stream);
 int tensor_sm100_copy(float *dst, const float *src, size_t n, void *stream);
 /* y[i] = alpha * x[i] + y[i], one fused multiply-add per element. */
 int tensor_sm100_axpy(size_t n, float alpha, const float *x, float *y, void *stream);
+/* y[i] = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))): the tanh approximation of GELU the reference uses. */
+int tensor_sm100_gelu_forward(const float *x, float *y, size_t n, void *stream);
+/* dx[i] = g[i] * d/dx of the above at x[i] (overwritten, like the reference). */
+int tensor_sm100_gelu_backward(const float *g, const float *x, float *dx, size_t n, void *stream);
 
 #ifdef __cplusplus
 }

@@ -53,6 +53,30 @@ def test_fill_copy_arange_axpy(pkg, n, offset):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("n,offset", [(1, 0), (1025, 1), (8 * 1024 * 3072 // 8, 0)])
+def test_gelu_forward_backward(pkg, n, offset):
+    """tanh-approximated GELU against its float64 evaluation (kernels/src/cuda/GeLU.cu:5-38)."""
+    L = pkg.lib()
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n + offset) * 2.5).astype(np.float32)
+    g = rng.standard_normal(n + offset).astype(np.float32)
+    xt, gt = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    y = torch.full((n + offset + 4,), -7.0, device="cuda")
+    dx = torch.full((n + offset + 4,), -7.0, device="cuda")
+    o = 4 * offset
+    assert L.tensor_sm100_gelu_forward(xt.data_ptr() + o, y.data_ptr() + o, n, stream()) == 0
+    assert L.tensor_sm100_gelu_backward(gt.data_ptr() + o, xt.data_ptr() + o, dx.data_ptr() + o, n, stream()) == 0
+    x64, g64 = x[offset:].astype(np.float64), g[offset:].astype(np.float64)
+    kb = np.sqrt(2.0 / np.pi)
+    t = np.tanh(kb * (x64 + 0.044715 * x64 ** 3))
+    y_ref = 0.5 * x64 * (1.0 + t)
+    d_ref = g64 * (0.5 * (1.0 + t) + 0.5 * x64 * (1.0 - t * t) * kb * (1.0 + 3.0 * 0.044715 * x64 ** 2))
+    assert np.abs(y[offset:offset + n].cpu().numpy() - y_ref).max() <= 2e-6 * max(1.0, np.abs(y_ref).max())
+    assert np.abs(dx[offset:offset + n].cpu().numpy() - d_ref).max() <= 4e-6 * max(1.0, np.abs(d_ref).max())
+    assert torch.all(y[offset + n:] == -7.0) and torch.all(dx[offset + n:] == -7.0)
+    torch.cuda.synchronize()
+
+
 def test_null_pointers(pkg):
     L = pkg.lib()
     assert L.tensor_sm100_fill(None, 4, 0.0, None) == -1
