@@ -58,6 +58,7 @@ struct __align__(1024) SmemT {
 struct Problem {
     int M, N, K;  // C is [M, N]; K is the contraction length
     int bn;       // tile width
+    int a_one, b_one;  // MN-major operand fetched with one 3-D copy per stage (else one copy per 32-row block)
     int tiles_m, tiles_n, splits, kb_total, kb_per_split, total;
 };
 
@@ -174,16 +175,24 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     // K-major: map {contraction, rows}, one box {32, 128}.  MN-major: map {rows, contraction},
                     // four boxes {32, 32}: blocks of 32 rows, each [32 contraction steps x 128 bytes].
                     if (kAMN) {
+                        if (p.a_one) {
+                            tma_load_4d(sm.a[st], &map_a, &sm.full[st], 0, kb * kBK, wk.m0 / 32, 0);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 4; i++)
-                            tma_load_4d(sm.a[st] + i * 4096, &map_a, &sm.full[st], wk.m0 + 32 * i, kb * kBK, 0, 0);
+                            for (int i = 0; i < 4; i++)
+                                tma_load_4d(sm.a[st] + i * 4096, &map_a, &sm.full[st], wk.m0 + 32 * i, kb * kBK, 0, 0);
+                        }
                     } else {
                         tma_load_4d(sm.a[st], &map_a, &sm.full[st], kb * kBK, wk.m0, 0, 0);
                     }
                     if (kBMN) {
+                        if (p.b_one) {
+                            tma_load_4d(sm.b[st], &map_b, &sm.full[st], 0, kb * kBK, wk.n0 / 32, 0);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < kBN / 32; i++)
-                            tma_load_4d(sm.b[st] + i * 4096, &map_b, &sm.full[st], wk.n0 + 32 * i, kb * kBK, 0, 0);
+                            for (int i = 0; i < kBN / 32; i++)
+                                tma_load_4d(sm.b[st] + i * 4096, &map_b, &sm.full[st], wk.n0 + 32 * i, kb * kBK, 0, 0);
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < kBN / 64; i++)  // the B map's box is 64 rows
@@ -424,6 +433,16 @@ int map_k_major(CUtensorMap *map, const float *base, int rows, int kc, int box_r
     const cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
     return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box);
 }
+// Operand read MN-major, whole tile in one copy: the matrix [kc, rows] seen as {32 values, kc, rows / 32 blocks}
+// with the block index as the slowest box dimension, box {32, 32, nblocks}: shared memory receives
+// [block][contraction step][32 values], the layout the descriptor expects.  rows % 32 == 0.
+int map_mn_major_blocks(CUtensorMap *map, const float *base, int kc, int rows, int nblocks) {
+    const cuuint64_t dims[4] = {32, (cuuint64_t)kc, (cuuint64_t)(rows / 32), 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)rows * 4, 128, (cuuint64_t)rows * 4 * (cuuint64_t)kc};
+    const cuuint32_t box[4] = {32, 32, (cuuint32_t)nblocks, 1};
+    return attn::encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
 // Operand read MN-major: matrix [kc, rows] row-major (rows contiguous, kc = contraction), boxes of 32 x 32.
 int map_mn_major(CUtensorMap *map, const float *base, int kc, int rows) {
     const cuuint64_t dims[4] = {(cuuint64_t)rows, (cuuint64_t)kc, 1, 1};
@@ -450,6 +469,7 @@ int map_out_planes(CUtensorMap *map, const void *base, int rows, int cols) {
 Problem make_problem(int M, int N, int K, int bn, int splits) {
     Problem p;
     p.M = M, p.N = N, p.K = K, p.bn = bn;
+    p.a_one = p.b_one = 0;
     p.tiles_m = (M + kBM - 1) / kBM;
     p.tiles_n = (N + bn - 1) / bn;
     p.kb_total = (K + kBK - 1) / kBK;
@@ -591,21 +611,26 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     if (dx) {
         // dx[M,K] = dy[M,N] . w[N,K]: contraction over N (rows of w past N read as zeros)
         if ((rc = map_k_major(&ma, g, M, np, 128)) != 0) return rc;
-        if ((rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
+        Problem pdx = make_problem(M, K, np, pick_bn(M, K, 1, sms), 1);
+        pdx.b_one = map_mn_major_blocks(&mb, w, N, K, pdx.bn / 32) == 0;
+        if (!pdx.b_one && (rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
         if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
-        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, make_problem(M, K, np, pick_bn(M, K, 1, sms), 1), status, s);
+        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, pdx, status, s);
         if (rc != 0) return rc;
     }
     if (dw) {
         // dw[N,K] += dy[M,N]^T . x[M,K]: contraction over M, split so that every SM has work (rows of the
         // result past N are dropped by the copy engine)
-        if ((rc = map_mn_major(&ma, g, M, np)) != 0) return rc;
-        if ((rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
-        if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
         const int bn = K % 256 == 0 ? 256 : (K % 192 == 0 ? 192 : 128);
         const int tiles = ((N + kBM - 1) / kBM) * ((K + bn - 1) / bn);
         const int splits = (2 * sms + tiles - 1) / tiles;  // about two work items per SM
-        rc = launch<true, true, 1>(ma, mb, mc, mc, nullptr, false, make_problem(N, K, M, bn, splits), status, s);
+        Problem pdw = make_problem(N, K, M, bn, splits);
+        pdw.a_one = map_mn_major_blocks(&ma, g, M, np, 4) == 0;
+        if (!pdw.a_one && (rc = map_mn_major(&ma, g, M, np)) != 0) return rc;
+        pdw.b_one = map_mn_major_blocks(&mb, x, M, K, bn / 32) == 0;
+        if (!pdw.b_one && (rc = map_mn_major(&mb, x, M, K)) != 0) return rc;
+        if ((rc = map_out_f32(&mc, dw, N, K)) != 0) return rc;
+        rc = launch<true, true, 1>(ma, mb, mc, mc, nullptr, false, pdw, status, s);
         if (rc != 0) return rc;
     }
     if (db) {
