@@ -194,9 +194,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                 tma_load_4d(sm.b[st] + i * 4096, &map_b, &sm.full[st], wk.n0 + 32 * i, kb * kBK, 0, 0);
                         }
                     } else {
-#pragma unroll
-                        for (int i = 0; i < kBN / 64; i++)  // the B map's box is 64 rows
-                            tma_load_4d(sm.b[st] + i * 8192, &map_b, &sm.full[st], kb * kBK, wk.n0 + 64 * i, 0, 0);
+                        tma_load_4d(sm.b[st], &map_b, &sm.full[st], kb * kBK, wk.n0, 0, 0);  // the B map's box is kBN rows
                     }
                 }
             }
@@ -562,8 +560,9 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     int rc = attn::device_status_word(&status);
     if (rc != ATTN_OK) return rc;
     CUtensorMap ma, mb, mc, mp;
+    const int bn = direct ? 256 : pick_bn(M, N, 1, sm_count());
     if ((rc = map_k_major(&ma, x, M, K, 128)) != 0) return rc;
-    if ((rc = map_k_major(&mb, w, N, K, 64)) != 0) return rc;
+    if ((rc = map_k_major(&mb, w, N, K, bn)) != 0) return rc;
     if (direct) {
         const Problem pd = make_problem(M, N, K, 256, 1);
         return launch_one<false, false, 0, 256, 4, false, true>(ma, mb, ma, ma, bias, pd, status,
@@ -572,7 +571,7 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     if ((rc = map_out_f32(&mc, y, M, N)) != 0) return rc;
     mp = mc;
     if (planes && (rc = map_out_planes(&mp, planes, M, N)) != 0) return rc;
-    const Problem p = make_problem(M, N, K, pick_bn(M, N, 1, sm_count()), 1);
+    const Problem p = make_problem(M, N, K, bn, 1);
     return launch<false, false, 0>(ma, mb, mc, mp, bias, planes != nullptr, p, status, static_cast<cudaStream_t>(stream));
 }
 
