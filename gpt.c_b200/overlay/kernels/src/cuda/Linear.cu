@@ -36,7 +36,7 @@ extern "C" void overlay_planes_offer(const float *y, void *planes, size_t bytes)
 }
 
 extern "C" void *overlay_planes_take(const float *y, size_t bytes) {
-    if (!g_offer_planes || g_offer_y != y || g_offer_bytes < bytes) return NULL;
+    if (!g_offer_planes || g_offer_y != y || g_offer_bytes != bytes) return NULL;
     void *p = g_offer_planes;
     g_offer_y = NULL;
     g_offer_planes = NULL;

@@ -12,7 +12,7 @@ extern "C" {
 
 // `planes` was allocated with alloc_cuda and holds `bytes` bytes of planes for the tensor at `y`.
 void overlay_planes_offer(const float *y, void *planes, size_t bytes);
-// Returns the planes offered for `y` when they hold at least `bytes` bytes (ownership passes to the
+// Returns the planes offered for `y` when they hold exactly `bytes` bytes (ownership passes to the
 // caller, who releases them with free_cuda), else NULL.
 void *overlay_planes_take(const float *y, size_t bytes);
 
