@@ -192,6 +192,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int niter = nt - jt;  // query tiles jt .. nt-1
 
     WaitCtx ctx{&sm.abort_flag, status};
+    pdl_launch_dependents();
     BWD_LIFE(0);
 
     if (threadIdx.x == 0) {
@@ -217,7 +218,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         mbar_init(&sm.kv_out_full, kComputeThreads);
         fence_barrier_init();
         // This thread is also the TMA producer: K, V and the first Q/dO half tiles are requested
-        // right away, while the other warps are still setting up.
+        // right away, while the other warps are still setting up (but not before the kernel that
+        // wrote them has completed).
+        pdl_wait();
         fence_proxy_async_smem();
         tma_prefetch_desc(&map_x);
         tma_prefetch_desc(&map_do);
@@ -242,6 +245,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         tmem_alloc(&sm.tmem_base, kTmemCols);
         tmem_relinquish();
     }
+    pdl_wait();  // every thread, before its first access to global memory
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -667,9 +671,8 @@ cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &ma
     const int nt = (T + kTile - 1) / kTile;
     const unsigned grid = (unsigned)(nt * B * H);
     const float scale = 0.125f;  // 1/sqrt(64)
-    attn_bwd_kernel<<<grid, kThreads, bwd_smem_bytes(), s>>>(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, scale,
-                                                             scale * 1.4426950408889634f, status);
-    return cudaGetLastError();
+    return launch_after_previous(attn_bwd_kernel, dim3(grid), dim3(kThreads), bwd_smem_bytes(), s, map_x, map_do, map_dx, lse,
+                                 delta, dqkv, B, T, H, scale, scale * 1.4426950408889634f, status);
 }
 
 }  // namespace attn

@@ -189,6 +189,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int nsteps = 2 * (qt + 1);  // key steps of 64 up to the end of the diagonal tile
 
     WaitCtx ctx{&sm.abort_flag, status};
+    pdl_launch_dependents();
     FWD_LIFE(0);
     FWD_PHASE(threadIdx.x == 128, 0);
 
@@ -209,7 +210,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         for (int i = 0; i < 4; i++) mbar_init(&sm.pair_bar[i], 64);
         fence_barrier_init();
         // This thread is also the Q/K producer: Q and the first two K steps are requested right
-        // away, while the other warps are still setting up.
+        // away, while the other warps are still setting up (but not before the kernel that wrote
+        // them has completed).
+        pdl_wait();
         fence_proxy_async_smem();
         tma_prefetch_desc(&map_x);
         const int xq = h * kD, xk = C + h * kD;
@@ -228,6 +231,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         tmem_alloc(&sm.tmem_base, kTmemCols);
         tmem_relinquish();
     }
+    pdl_wait();  // every thread, before its first access to global memory
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -477,9 +481,8 @@ cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map
     const int out_maps = map_out ? (map_copy && out_copy ? 2 : 1) : 0;
     const CUtensorMap &mo = map_out ? *map_out : map_x;  // unused by the kernel when out_maps == 0
     const CUtensorMap &mc = out_maps == 2 ? *map_copy : mo;
-    attn_fwd_kernel<<<grid, kThreads, fwd_smem_bytes(), s>>>(map_x, mo, mc, out_maps, out, out_copy, lse, B, T, H,
-                                                             scale_log2, status);
-    return cudaGetLastError();
+    return launch_after_previous(attn_fwd_kernel, dim3(grid), dim3(kThreads), fwd_smem_bytes(), s, map_x, mo, mc, out_maps, out,
+                                 out_copy, lse, B, T, H, scale_log2, status);
 }
 
 }  // namespace attn

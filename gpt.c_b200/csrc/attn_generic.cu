@@ -6,6 +6,7 @@
 // D = 3 case of the reference's tests/test_self_attention.py).  They replace the same
 // reference code as the fast path: kernels/src/cuda/Attention.cu:170-324 of gpt.c.
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 namespace attn {
 
@@ -41,6 +42,8 @@ struct XSplit {
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) split_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ hi,
                                                      __nv_bfloat16 *__restrict__ lo, size_t n) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t n8 = n / 8;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < n8; v += stride) {
@@ -111,6 +114,8 @@ __global__ void __launch_bounds__(256) bwd_prepare64_kernel(const float *__restr
                                                              float *__restrict__ delta, __nv_bfloat16 *__restrict__ dhi,
                                                              __nv_bfloat16 *__restrict__ dlo, float *__restrict__ dq_zero,
                                                              int B, int T, int H) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const int C = H * 64;
     const size_t nvec = (size_t)B * T * C / 8;  // multiple of 8, so whole groups of 8 lanes stay together
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -332,8 +337,7 @@ cudaError_t launch_split(const float *x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, s
     size_t blocks = (work + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks == 0) blocks = 1;
-    split_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, hi, lo, n);
-    return cudaGetLastError();
+    return launch_after_previous(split_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, hi, lo, n);
 }
 
 cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta, __nv_bfloat16 *dhi,
@@ -342,8 +346,8 @@ cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta
         const size_t nvec = (size_t)B * T * H * 8;
         size_t blocks = (nvec + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        bwd_prepare64_kernel<<<(unsigned)blocks, 256, 0, s>>>(dout, out, delta, dhi, dlo, dq_zero, B, T, H);
-        return cudaGetLastError();
+        return launch_after_previous(bwd_prepare64_kernel, dim3((unsigned)blocks), dim3(256), 0, s, dout, out, delta, dhi,
+                                     dlo, dq_zero, B, T, H);
     }
     const size_t rows = (size_t)B * T * H;
     size_t blocks = (rows + 7) / 8;

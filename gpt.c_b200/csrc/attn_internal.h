@@ -44,6 +44,24 @@ cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
                                  const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s);
 
+// Launches `kernel` so that it may begin (up to its pdl_wait(), tc05.cuh) while the previous kernel of the
+// stream is still running: its launch latency and set-up overlap that kernel's tail.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_previous(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                         Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Helpers shared with the Linear kernels (linear_sm100.cu).
 // cuTensorMapEncodeTiled with the given swizzle, no interleave, no L2 promotion, zero fill; the encoder
 // is resolved by attn_sm100_init.  Returns 0 or a cudaError_t.

@@ -33,6 +33,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // ------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with launch_after_previous() (attn_internal.h) may
+// start while the kernel before it in the stream is still running.  It must not touch global memory
+// before pdl_wait() (returns once the previous kernel has completed and its writes are visible);
+// pdl_launch_dependents() lets the kernel after this one start its own set-up.  Both are no-ops for a
+// kernel launched the ordinary way.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
 // mbarrier
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
