@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 #include "../../include/adamw_sm100.h"
 
@@ -45,6 +46,8 @@ __device__ __forceinline__ void update(float &p, float g, float &m, float &v, fl
 __global__ void __launch_bounds__(kThreads) adamw_kernel(const Entry *__restrict__ entries, const Chunk *__restrict__ chunks,
                                                          float lr, float beta1, float beta2, float wd, float eps, float c1,
                                                          float c2) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const Chunk ck = chunks[blockIdx.x];
     const Entry e = entries[ck.tensor];
     const int end = min(e.len, ck.start + kChunk);
@@ -131,8 +134,8 @@ int adamw_sm100_step(float *const *params, float *const *grads, float *const *m,
     if (c.nchunks == 0) return ATTN_OK;
     const float c1 = 1.0f / (1.0f - powf(beta1, (float)step));
     const float c2 = 1.0f / (1.0f - powf(beta2, (float)step));
-    adamw_kernel<<<c.nchunks, kThreads, 0, s>>>(c.d_entries, c.d_chunks, lr, beta1, beta2, weight_decay, eps, c1, c2);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(adamw_kernel, dim3(c.nchunks), dim3(kThreads), 0, s, c.d_entries, c.d_chunks, lr, beta1,
+                                            beta2, weight_decay, eps, c1, c2);
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@
 // columns in registers over all the rows it visits; a block adds them up in shared memory and issues
 // one atomicAdd per column, which cuts the atomics from rows x C to blocks x C.
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 #include "../../include/layernorm_sm100.h"
 
@@ -33,6 +34,8 @@ __global__ void __launch_bounds__(kThreads) ln_forward_kernel(const float *__res
                                                                const float *__restrict__ b, float eps,
                                                                float *__restrict__ mean, float *__restrict__ rstd,
                                                                float *__restrict__ y, int rows, int C) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * kWarpsPerBlock;
@@ -83,6 +86,8 @@ __global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__re
                                                                 const float *__restrict__ rstd, const float *__restrict__ w,
                                                                 float *__restrict__ dw, float *__restrict__ db,
                                                                 float *__restrict__ dx, int rows, int C) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     extern __shared__ float4 red[];  // [kWarpsPerBlock][nvec] partial sums, used twice (dW, then db)
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warp = blockIdx.x * kWarpsPerBlock + wid;
@@ -173,8 +178,8 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 template <int kNV>
 int launch_fwd(const float *x, const float *w, const float *b, float eps, float *mean, float *rstd, float *y, int rows, int C,
                cudaStream_t s) {
-    ln_forward_kernel<kNV><<<grid_for(rows, 12), kThreads, 0, s>>>(x, w, b, eps, mean, rstd, y, rows, C);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(ln_forward_kernel<kNV>, dim3(grid_for(rows, 12)), dim3(kThreads), 0, s, x, w, b, eps,
+                                            mean, rstd, y, rows, C);
 }
 template <int kNV>
 int launch_bwd(const float *dy, const float *x, const float *mean, const float *rstd, const float *w, float *dw, float *db,
@@ -185,8 +190,8 @@ int launch_bwd(const float *dy, const float *x, const float *mean, const float *
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<grid_for(rows, 3), kThreads, smem, s>>>(dy, x, mean, rstd, w, dw, db, dx, rows, C);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(kernel, dim3(grid_for(rows, 3)), dim3(kThreads), smem, s, dy, x, mean, rstd, w, dw,
+                                            db, dx, rows, C);
 }
 
 }  // namespace

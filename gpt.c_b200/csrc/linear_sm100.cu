@@ -132,6 +132,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     WaitCtx ctx{&sm.abort_flag, status};
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
@@ -151,6 +152,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         tmem_alloc(&sm.tmem_base, kTmemCols);
         tmem_relinquish();
     }
+    pdl_wait();  // every thread, before its first access to global memory
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -378,6 +380,8 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 // share of the rows; four loads are in flight per thread.  N is a multiple of 4.
 __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ db, int M, int N,
                                                         int pitch) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     __shared__ float4 part[8][32];
     const int lane = threadIdx.x & 31, rl = threadIdx.x >> 5;
     const int col = blockIdx.x * 128 + 4 * lane;
@@ -414,6 +418,8 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict_
 // outputs of layers whose feature count is not a multiple of 4 (the vocabulary projection).
 __global__ void __launch_bounds__(256) pad_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, int M, int N,
                                                        int Np) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t total = (size_t)M * Np, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const size_t m = i / Np;
@@ -519,8 +525,8 @@ int launch_one(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &
     }
     const int sms = sm_count();
     const int grid = p.total < sms ? p.total : sms;
-    kernel<<<grid, kThreads, sizeof(Smem), s>>>(ma, mb, mc, mp, bias, c_direct, p, status);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(kernel, dim3(grid), dim3(kThreads), sizeof(Smem), s, ma, mb, mc, mp, bias, c_direct, p,
+                                            status);
 }
 
 // Pipeline depth by what fits in 227 KiB next to the output staging tile.
@@ -602,8 +608,9 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     const int sms = sm_count();
     const float *g = dy;  // [M, np] from here on
     if (padded) {
-        pad_rows_kernel<<<sms * 16, 256, 0, s>>>(static_cast<float *>(scratch), dy, M, N, np);
-        if ((rc = (int)cudaGetLastError()) != 0) return rc;
+        rc = (int)attn::launch_after_previous(pad_rows_kernel, dim3(sms * 16), dim3(256), 0, s, static_cast<float *>(scratch), dy, M,
+                                              N, np);
+        if (rc != 0) return rc;
         g = static_cast<const float *>(scratch);
     }
     CUtensorMap ma, mb, mc;
@@ -635,8 +642,7 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     if (db) {
         const int by = M >= 2048 ? 32 : (M + 63) / 64;  // rows per block column: at least 8 per row lane
         dim3 grid((unsigned)((N + 127) / 128), (unsigned)by);
-        bias_grad_kernel<<<grid, 256, 0, s>>>(g, db, M, N, np);
-        rc = (int)cudaGetLastError();
+        rc = (int)attn::launch_after_previous(bias_grad_kernel, grid, dim3(256), 0, s, g, db, M, N, np);
     }
     return rc;
 }

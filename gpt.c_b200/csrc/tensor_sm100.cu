@@ -7,6 +7,7 @@
 // tanh-approximated GELU of the MLP (kernels/src/cuda/GeLU.cu), forward and backward.
 // All of them are pure HBM traffic; the bound is the copy bandwidth.
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 #include "../../include/tensor_sm100.h"
 
@@ -26,6 +27,8 @@ int grid_for(size_t work_items) {
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 __global__ void __launch_bounds__(kThreads) fill_kernel(float *__restrict__ p, size_t n, float v) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t n4 = n / 4;
     const float4 v4 = make_float4(v, v, v, v);
@@ -34,11 +37,15 @@ __global__ void __launch_bounds__(kThreads) fill_kernel(float *__restrict__ p, s
 }
 
 __global__ void __launch_bounds__(kThreads) fill_scalar_kernel(float *__restrict__ p, size_t n, float v) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
 }
 
 __global__ void __launch_bounds__(kThreads) arange_kernel(float *__restrict__ p, size_t n, int start, int step) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         p[i] = (float)(start + step * (int)i);  // integer arithmetic first, like the reference
@@ -46,6 +53,8 @@ __global__ void __launch_bounds__(kThreads) arange_kernel(float *__restrict__ p,
 
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads) copy_kernel(float *__restrict__ dst, const float *__restrict__ src, size_t n) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (kVec) {
         const size_t n4 = n / 4;
@@ -65,6 +74,8 @@ __global__ void __launch_bounds__(kThreads) copy_kernel(float *__restrict__ dst,
 
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads) axpy_kernel(size_t n, float alpha, const float *__restrict__ x, float *__restrict__ y) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (kVec) {
         const size_t n4 = n / 4;
@@ -97,6 +108,8 @@ __device__ __forceinline__ float gelu_bwd(float g, float x) {
 
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads) gelu_forward_kernel(const float *__restrict__ x, float *__restrict__ y, size_t n) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (kVec) {
         const size_t n4 = n / 4;
@@ -113,6 +126,8 @@ __global__ void __launch_bounds__(kThreads) gelu_forward_kernel(const float *__r
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads) gelu_backward_kernel(const float *__restrict__ g, const float *__restrict__ x,
                                                                  float *__restrict__ dx, size_t n) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (kVec) {
         const size_t n4 = n / 4;
@@ -139,17 +154,16 @@ int tensor_sm100_fill(float *p, size_t n, float value, void *stream) {
     if (!p) return ATTN_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (value == 0.0f && !signbit(value)) return (int)cudaMemsetAsync(p, 0, n * sizeof(float), s);
-    if (aligned16(p)) fill_kernel<<<grid_for(n / 4 + 1), kThreads, 0, s>>>(p, n, value);
-    else fill_scalar_kernel<<<grid_for(n), kThreads, 0, s>>>(p, n, value);
-    return (int)cudaGetLastError();
+    if (aligned16(p)) return (int)attn::launch_after_previous(fill_kernel, dim3(grid_for(n / 4 + 1)), dim3(kThreads), 0, s, p, n, value);
+    return (int)attn::launch_after_previous(fill_scalar_kernel, dim3(grid_for(n)), dim3(kThreads), 0, s, p, n, value);
 }
 
 int tensor_sm100_arange(float *p, size_t n, int start, int step, void *stream) {
     using namespace tens;
     if (n == 0) return ATTN_OK;
     if (!p) return ATTN_ERR_NULL;
-    arange_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, n, start, step);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(arange_kernel, dim3(grid_for(n)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p,
+                                            n, start, step);
 }
 
 int tensor_sm100_copy(float *dst, const float *src, size_t n, void *stream) {
@@ -157,9 +171,9 @@ int tensor_sm100_copy(float *dst, const float *src, size_t n, void *stream) {
     if (n == 0) return ATTN_OK;
     if (!dst || !src) return ATTN_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (aligned16(dst) && aligned16(src)) copy_kernel<true><<<grid_for(n / 8 + 1), kThreads, 0, s>>>(dst, src, n);
-    else copy_kernel<false><<<grid_for(n), kThreads, 0, s>>>(dst, src, n);
-    return (int)cudaGetLastError();
+    if (aligned16(dst) && aligned16(src))
+        return (int)attn::launch_after_previous(copy_kernel<true>, dim3(grid_for(n / 8 + 1)), dim3(kThreads), 0, s, dst, src, n);
+    return (int)attn::launch_after_previous(copy_kernel<false>, dim3(grid_for(n)), dim3(kThreads), 0, s, dst, src, n);
 }
 
 int tensor_sm100_axpy(size_t n, float alpha, const float *x, float *y, void *stream) {
@@ -167,9 +181,9 @@ int tensor_sm100_axpy(size_t n, float alpha, const float *x, float *y, void *str
     if (n == 0) return ATTN_OK;
     if (!x || !y) return ATTN_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (aligned16(x) && aligned16(y)) axpy_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(n, alpha, x, y);
-    else axpy_kernel<false><<<grid_for(n), kThreads, 0, s>>>(n, alpha, x, y);
-    return (int)cudaGetLastError();
+    if (aligned16(x) && aligned16(y))
+        return (int)attn::launch_after_previous(axpy_kernel<true>, dim3(grid_for(n / 4 + 1)), dim3(kThreads), 0, s, n, alpha, x, y);
+    return (int)attn::launch_after_previous(axpy_kernel<false>, dim3(grid_for(n)), dim3(kThreads), 0, s, n, alpha, x, y);
 }
 
 int tensor_sm100_gelu_forward(const float *x, float *y, size_t n, void *stream) {
@@ -177,9 +191,9 @@ int tensor_sm100_gelu_forward(const float *x, float *y, size_t n, void *stream) 
     if (n == 0) return ATTN_OK;
     if (!x || !y) return ATTN_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (aligned16(x) && aligned16(y)) gelu_forward_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(x, y, n);
-    else gelu_forward_kernel<false><<<grid_for(n), kThreads, 0, s>>>(x, y, n);
-    return (int)cudaGetLastError();
+    if (aligned16(x) && aligned16(y))
+        return (int)attn::launch_after_previous(gelu_forward_kernel<true>, dim3(grid_for(n / 4 + 1)), dim3(kThreads), 0, s, x, y, n);
+    return (int)attn::launch_after_previous(gelu_forward_kernel<false>, dim3(grid_for(n)), dim3(kThreads), 0, s, x, y, n);
 }
 
 int tensor_sm100_gelu_backward(const float *g, const float *x, float *dx, size_t n, void *stream) {
@@ -187,9 +201,9 @@ int tensor_sm100_gelu_backward(const float *g, const float *x, float *dx, size_t
     if (n == 0) return ATTN_OK;
     if (!g || !x || !dx) return ATTN_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (aligned16(g) && aligned16(x) && aligned16(dx)) gelu_backward_kernel<true><<<grid_for(n / 4 + 1), kThreads, 0, s>>>(g, x, dx, n);
-    else gelu_backward_kernel<false><<<grid_for(n), kThreads, 0, s>>>(g, x, dx, n);
-    return (int)cudaGetLastError();
+    if (aligned16(g) && aligned16(x) && aligned16(dx))
+        return (int)attn::launch_after_previous(gelu_backward_kernel<true>, dim3(grid_for(n / 4 + 1)), dim3(kThreads), 0, s, g, x, dx, n);
+    return (int)attn::launch_after_previous(gelu_backward_kernel<false>, dim3(grid_for(n)), dim3(kThreads), 0, s, g, x, dx, n);
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@
 // one online pass, then the write pass re-reads the row (200 KB, still in L2): 8 bytes of HBM traffic per
 // element.  Backward: 12 bytes per element (dout is read-modify-write).
 #include "attn_internal.h"
+#include "tc05.cuh"
 
 #include "../../include/xent_sm100.h"
 
@@ -35,6 +36,8 @@ __global__ void __launch_bounds__(kThreads) xent_forward_kernel(const float *__r
                                                                 const float *__restrict__ targets,
                                                                 float *__restrict__ logsm, float *__restrict__ loss,
                                                                 int rows, int C) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     __shared__ float s_m[kThreads / 32], s_s[kThreads / 32];
     __shared__ float s_shift;
     const int r = blockIdx.x;
@@ -79,6 +82,8 @@ __global__ void __launch_bounds__(kThreads) xent_backward_kernel(const float *__
                                                                  const float *__restrict__ targets,
                                                                  const float *__restrict__ logsm, float *__restrict__ dout,
                                                                  int rows, int C) {
+    tc05::pdl_launch_dependents();
+    tc05::pdl_wait();
     __shared__ float s_part[kThreads / 32];
     __shared__ float s_total;
     const int r = blockIdx.x;
@@ -113,17 +118,15 @@ extern "C" {
 int xent_sm100_forward(const float *logits, const float *targets, float *logsm, float *loss, int rows, int C, void *stream) {
     if (!logits || !targets || !logsm || !loss) return ATTN_ERR_NULL;
     if (rows <= 0 || C <= 0) return ATTN_ERR_SHAPE;
-    xent::xent_forward_kernel<<<rows, xent::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, targets, logsm, loss,
-                                                                                               rows, C);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(xent::xent_forward_kernel, dim3(rows), dim3(xent::kThreads), 0,
+                                            static_cast<cudaStream_t>(stream), logits, targets, logsm, loss, rows, C);
 }
 
 int xent_sm100_backward(const float *g, const float *targets, const float *logsm, float *dout, int rows, int C, void *stream) {
     if (!g || !targets || !logsm || !dout) return ATTN_ERR_NULL;
     if (rows <= 0 || C <= 0) return ATTN_ERR_SHAPE;
-    xent::xent_backward_kernel<<<rows, xent::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, targets, logsm, dout, rows,
-                                                                                                C);
-    return (int)cudaGetLastError();
+    return (int)attn::launch_after_previous(xent::xent_backward_kernel, dim3(rows), dim3(xent::kThreads), 0,
+                                            static_cast<cudaStream_t>(stream), g, targets, logsm, dout, rows, C);
 }
 
 }  // extern "C"
