@@ -28,6 +28,7 @@
 #include "tc05.cuh"
 
 #include "../../include/linear_sm100.h"
+#include "../../include/tensor_sm100.h"
 
 namespace lin {
 namespace {
@@ -60,6 +61,7 @@ struct Problem {
     int bn;       // tile width
     int a_one, b_one;  // MN-major operand fetched with one 3-D copy per stage (else one copy per 32-row block)
     int tiles_m, tiles_n, splits, kb_total, kb_per_split, total;
+    int m_fast;  // consecutive work items walk down the rows of C (else along its columns)
 };
 
 enum Site : int {
@@ -104,7 +106,10 @@ struct Work {
 __device__ __forceinline__ Work decode(const Problem &p, int w) {
     const int split = w % p.splits;
     const int t = w / p.splits;
-    const int tn = t % p.tiles_n, tm = t / p.tiles_n;
+    // The operand whose tile index changes slowest is read from HBM once; the other one is streamed again for
+    // every step of the slow index and has to live in L2.  The host picks the order by operand size.
+    const int tn = p.m_fast ? t / p.tiles_m : t % p.tiles_n;
+    const int tm = p.m_fast ? t % p.tiles_m : t / p.tiles_n;
     Work r;
     r.m0 = tm * kBM;
     r.n0 = tn * p.bn;
@@ -420,11 +425,52 @@ __global__ void __launch_bounds__(256) pad_rows_kernel(float *__restrict__ dst, 
                                                        int Np) {
     tc05::pdl_launch_dependents();
     tc05::pdl_wait();
-    const size_t total = (size_t)M * Np, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t m = i / Np;
-        const int j = (int)(i - m * Np);
-        dst[i] = j < N ? __ldcs(src + m * N + j) : 0.f;
+    // One block per row at a time.  The source row starts `o` floats past a 16-byte boundary (src itself is
+    // 16-byte aligned): every thread loads the two aligned 16-byte words around its four values and picks them
+    // out, so that loads and stores are all 16 bytes wide (the neighbour thread's copy of a word comes from L1).
+    // Four such pairs are in flight per thread.  Words that reach past the end of src are read value by value.
+    const size_t total = (size_t)M * N;
+    const int nv = Np >> 2;
+    auto load_word = [&](size_t at) -> float4 {
+        if (at + 3 < total) return __ldg(reinterpret_cast<const float4 *>(src + at));
+        float4 t;
+        t.x = at < total ? src[at] : 0.f;
+        t.y = at + 1 < total ? src[at + 1] : 0.f;
+        t.z = at + 2 < total ? src[at + 2] : 0.f;
+        t.w = at + 3 < total ? src[at + 3] : 0.f;
+        return t;
+    };
+    constexpr int kU = 4;
+    for (int m = blockIdx.x; m < M; m += gridDim.x) {
+        const size_t start = (size_t)m * N;
+        const int o = (int)(start & 3);
+        const size_t base = start - o;  // multiple of 4
+        float4 *out = reinterpret_cast<float4 *>(dst + (size_t)m * Np);
+        for (int j0 = threadIdx.x; j0 < nv; j0 += 256 * kU) {
+            float4 a[kU], b[kU];
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                const int j4 = j0 + 256 * u;
+                a[u] = b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j4 < nv) {
+                    a[u] = load_word(base + 4 * (size_t)j4);
+                    if (o != 0) b[u] = load_word(base + 4 * (size_t)(j4 + 1));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                const int j4 = j0 + 256 * u;
+                if (j4 >= nv) continue;
+                const float v[8] = {a[u].x, a[u].y, a[u].z, a[u].w, b[u].x, b[u].y, b[u].z, b[u].w};
+                float r[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float pick = o == 0 ? v[e] : (o == 1 ? v[e + 1] : (o == 2 ? v[e + 2] : v[e + 3]));
+                    r[e] = 4 * j4 + e < N ? pick : 0.f;
+                }
+                __stcs(out + j4, make_float4(r[0], r[1], r[2], r[3]));
+            }
+        }
     }
 }
 
@@ -474,6 +520,7 @@ Problem make_problem(int M, int N, int K, int bn, int splits) {
     Problem p;
     p.M = M, p.N = N, p.K = K, p.bn = bn;
     p.a_one = p.b_one = 0;
+    p.m_fast = 0;
     p.tiles_m = (M + kBM - 1) / kBM;
     p.tiles_n = (N + bn - 1) / bn;
     p.kb_total = (K + kBK - 1) / kBK;
@@ -545,6 +592,29 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, 
     return launch_one<kAMN, kBMN, kEpi, 128, 6, false>(ma, mb, mc, mp, bias, p, status, s);
 }
 
+// C[M, N] = A[M, K] . B[N, K]^T: true when B (the weight) is too large to stay in L2 while every tile row of
+// C passes over it and A is the smaller operand; the work items then run down the rows of C, so that B is read
+// from HBM once and A (small) is what stays in L2.  (The vocabulary projection: B is 154 MB, A 25 MB.)
+int stream_rows_of_c(int M, int N, int K) {
+    const size_t a_bytes = (size_t)M * K * 4, b_bytes = (size_t)N * K * 4;
+    return b_bytes > ((size_t)48 << 20) && b_bytes > a_bytes ? 1 : 0;
+}
+
+// Number of pieces the contraction of a [M, N] result is cut into when it is very long and the tiles do not
+// fill the SMs evenly (dx of the vocabulary projection: 192 tiles on 148 SMs, 1571 steps each).  Each piece
+// pays a fixed charge for its epilogue; 1 = no split.
+int pick_splits(int tiles, int kb_total, int sms) {
+    if (kb_total < 512) return 1;
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= 8; s++) {
+        const long long rounds = ((long long)tiles * s + sms - 1) / sms;
+        const long long cost = rounds * ((kb_total + s - 1) / s + 24);
+        if (best_cost < 0 || cost < best_cost) best = s, best_cost = cost;
+    }
+    return best;
+}
+
 bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
 
 }  // namespace
@@ -570,14 +640,16 @@ int linear_sm100_forward(const float *x, const float *w, const float *bias, floa
     if ((rc = map_k_major(&ma, x, M, K, 128)) != 0) return rc;
     if ((rc = map_k_major(&mb, w, N, K, bn)) != 0) return rc;
     if (direct) {
-        const Problem pd = make_problem(M, N, K, 256, 1);
+        Problem pd = make_problem(M, N, K, 256, 1);
+        pd.m_fast = stream_rows_of_c(M, N, K);
         return launch_one<false, false, 0, 256, 4, false, true>(ma, mb, ma, ma, bias, pd, status,
                                                                 static_cast<cudaStream_t>(stream), y);
     }
     if ((rc = map_out_f32(&mc, y, M, N)) != 0) return rc;
     mp = mc;
     if (planes && (rc = map_out_planes(&mp, planes, M, N)) != 0) return rc;
-    const Problem p = make_problem(M, N, K, bn, 1);
+    Problem p = make_problem(M, N, K, bn, 1);
+    p.m_fast = stream_rows_of_c(M, N, K);
     return launch<false, false, 0>(ma, mb, mc, mp, bias, planes != nullptr, p, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -617,11 +689,30 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     if (dx) {
         // dx[M,K] = dy[M,N] . w[N,K]: contraction over N (rows of w past N read as zeros)
         if ((rc = map_k_major(&ma, g, M, np, 128)) != 0) return rc;
-        Problem pdx = make_problem(M, K, np, pick_bn(M, K, 1, sms), 1);
+        int bn_dx = pick_bn(M, K, 1, sms), splits_dx = 1;
+        if (np / kBK >= 512) {  // very long contraction: tile width and number of pieces together
+            const int cand[3] = {256, 192, 128};
+            long long best_cost = -1;
+            for (int i = 0; i < 3; i++) {
+                if (cand[i] > 128 && K < cand[i]) continue;
+                const int tiles = ((M + kBM - 1) / kBM) * ((K + cand[i] - 1) / cand[i]);
+                const int sp = pick_splits(tiles, np / kBK, sms);
+                const long long rounds = ((long long)tiles * sp + sms - 1) / sms;
+                const long long cost = rounds * ((np / kBK + sp - 1) / sp + 24) * (cand[i] + 192);
+                if (best_cost < 0 || cost < best_cost) best_cost = cost, bn_dx = cand[i], splits_dx = sp;
+            }
+        }
+        Problem pdx = make_problem(M, K, np, bn_dx, splits_dx);
         pdx.b_one = map_mn_major_blocks(&mb, w, N, K, pdx.bn / 32) == 0;
         if (!pdx.b_one && (rc = map_mn_major(&mb, w, N, K)) != 0) return rc;
         if ((rc = map_out_f32(&mc, dx, M, K)) != 0) return rc;
-        rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, pdx, status, s);
+        if (pdx.splits > 1) {
+            // the pieces of the contraction add into dx with bulk reductions: start from zeros
+            if ((rc = tensor_sm100_fill(dx, (size_t)M * K, 0.f, stream)) != 0) return rc;
+            rc = launch<false, true, 1>(ma, mb, mc, mc, nullptr, false, pdx, status, s);
+        } else {
+            rc = launch<false, true, 0>(ma, mb, mc, mc, nullptr, false, pdx, status, s);
+        }
         if (rc != 0) return rc;
     }
     if (dw) {

@@ -7,10 +7,13 @@
 //   backward  dout[r, target_r] = -g[r] / rows;  s = sum_j dout[r, j];  dout[r, j] -= exp(logsm[r, j]) * s
 // (the backward works on whatever dout holds, like the reference, whose layer hands in zeros).
 //
-// One block of 512 threads per row; the rows of a [rows, 50257] tensor start on 4-byte boundaries only,
+// One block of 1024 threads per row; the rows of a [rows, 50257] tensor start on 4-byte boundaries only,
 // so loads and stores are 4 bytes wide but fully coalesced.  Forward: maximum and sum of exponentials in
-// one online pass, then the write pass re-reads the row (200 KB, still in L2): 8 bytes of HBM traffic per
-// element.  Backward: 12 bytes per element (dout is read-modify-write).
+// one online pass, then the write pass re-reads the row (200 KB): 8 bytes of HBM traffic per element when the
+// re-read hits L2.  The forward loops keep eight loads per thread in flight: with one load per trip, which is
+// what the dependent maximum / sum update compiles to, the pass was bound by memory latency, not bandwidth.
+// (The backward loops have independent trips and gained nothing from the same change.)
+// Backward: 12 bytes per element (dout is read-modify-write; its second read hits L2 the same way).
 #include "attn_internal.h"
 #include "tc05.cuh"
 
@@ -19,7 +22,8 @@
 namespace xent {
 namespace {
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 1024;
+constexpr int kBatch = 8;  // independent loads per thread and loop trip
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -45,14 +49,22 @@ __global__ void __launch_bounds__(kThreads) xent_forward_kernel(const float *__r
     float *y = logsm + (size_t)r * C;
     // online maximum / sum of exponentials
     float m = -INFINITY, s = 0.f;
-    for (int j = threadIdx.x; j < C; j += kThreads) {
-        const float v = x[j];
-        if (v > m) {
-            s = s * __expf(m - v) + 1.0f;  // exp(-inf) = 0 on the first element
-            m = v;
-        } else {
-            s += __expf(v - m);
+    for (int j0 = threadIdx.x; j0 < C; j0 += kThreads * kBatch) {
+        float v[kBatch];  // kBatch loads in flight per thread: the pass is bound by HBM latency otherwise
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int j = j0 + u * kThreads;
+            v[u] = j < C ? __ldg(x + j) : -INFINITY;
         }
+        float bm = v[0];
+#pragma unroll
+        for (int u = 1; u < kBatch; u++) bm = fmaxf(bm, v[u]);
+        if (bm > m) {
+            s *= __expf(m - bm);  // exp(-inf) = 0 on the first batch
+            m = bm;
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) s += __expf(v[u] - m);  // exp(-inf) = 0 past the end of the row
     }
     // combine (m, s) pairs across the warp, then across the block
     const float wm = warp_max(m);
@@ -71,7 +83,19 @@ __global__ void __launch_bounds__(kThreads) xent_forward_kernel(const float *__r
     }
     __syncthreads();
     const float shift = s_shift;
-    for (int j = threadIdx.x; j < C; j += kThreads) y[j] = x[j] - shift;
+    for (int j0 = threadIdx.x; j0 < C; j0 += kThreads * kBatch) {
+        float v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int j = j0 + u * kThreads;
+            v[u] = j < C ? __ldg(x + j) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int j = j0 + u * kThreads;
+            if (j < C) y[j] = v[u] - shift;
+        }
+    }
     if (threadIdx.x == 0) {
         const int t = (int)targets[r];
         atomicAdd(loss, -(x[t] - shift) / (float)rows);

@@ -24,6 +24,9 @@ SHAPES = [
     (1000, 3072, 768),             # MLP up-projection shape
     (260, 50257, 768),             # vocabulary projection: rows of y not 16-byte aligned, plain stores
     (130, 1001, 64),               # the same path with a ragged last tile in every direction
+    (70, 95, 64),                  # 31 of 32 columns in the last block: the padded copy of dy reads its last word alone
+    (70, 94, 32),                  # rows of dy start 0 or 2 floats past a 16-byte boundary
+    (9, 16415, 32),                # long contraction for dx (513 steps): cut into pieces that add into a zeroed dx
 ]
 
 
