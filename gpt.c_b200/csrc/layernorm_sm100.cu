@@ -11,6 +11,8 @@
 // every tensor is read once.  In the backward each warp also carries the dW / db partial sums of its
 // columns in registers over all the rows it visits; a block adds them up in shared memory and issues
 // one atomicAdd per column, which cuts the atomics from rows x C to blocks x C.
+#include <cooperative_groups.h>
+
 #include "attn_internal.h"
 #include "tc05.cuh"
 
@@ -19,8 +21,11 @@
 namespace ln {
 namespace {
 
+namespace cg = cooperative_groups;
+
 constexpr int kWarpsPerBlock = 4;  // small blocks: the backward needs ~140 registers per thread at C = 768
 constexpr int kThreads = kWarpsPerBlock * 32;
+constexpr int kCluster = 4;  // blocks whose column sums are combined before the atomics (backward)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -81,14 +86,14 @@ __global__ void __launch_bounds__(kThreads) ln_forward_kernel(const float *__res
 }
 
 template <int kNV>
-__global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__restrict__ dy, const float *__restrict__ x,
+__global__ void __launch_bounds__(kThreads, (kNV <= 6 ? 4 : 1)) ln_backward_kernel(const float *__restrict__ dy, const float *__restrict__ x,
                                                                 const float *__restrict__ mean,
                                                                 const float *__restrict__ rstd, const float *__restrict__ w,
                                                                 float *__restrict__ dw, float *__restrict__ db,
                                                                 float *__restrict__ dx, int rows, int C) {
     tc05::pdl_launch_dependents();
     tc05::pdl_wait();
-    extern __shared__ float4 red[];  // [kWarpsPerBlock][nvec] partial sums, used twice (dW, then db)
+    extern __shared__ float4 red[];  // [kWarpsPerBlock][nvec] partial sums, used twice (dW, then db), then [2][nvec]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warp = blockIdx.x * kWarpsPerBlock + wid;
     const int nwarps = gridDim.x * kWarpsPerBlock;
@@ -106,7 +111,13 @@ __global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__re
         const float4 *gr = reinterpret_cast<const float4 *>(dy + (size_t)row * C);
         const float a = rstd[row], mu = mean[row];
         const float nb = -a * mu;
+        float4 *dr = reinterpret_cast<float4 *>(dx + (size_t)row * C);
         float4 xv[kNV], gv[kNV];
+        // dx is accumulated into.  Fetching its old values together with x and dy (one trip to memory per row
+        // instead of two) was measured and is no faster: it costs 40 registers, and the kernel is bound by how
+        // many warps are in flight.
+        constexpr bool kEarly = false;
+        float4 ov[kEarly ? kNV : 1];
         float ds = 0.f, dbs = 0.f;
 #pragma unroll
         for (int i = 0; i < kNV; i++) {
@@ -114,6 +125,7 @@ __global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__re
             const bool in = c < nvec;
             xv[i] = in ? __ldcs(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             gv[i] = in ? __ldcs(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (kEarly) ov[i] = in ? dr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
             const float4 wv = in ? __ldg(w4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             // from here on gv holds dy * w (what the input gradient needs); dy itself goes into the sums first
             gb[i].x += gv[i].x, gb[i].y += gv[i].y, gb[i].z += gv[i].z, gb[i].w += gv[i].w;
@@ -127,22 +139,23 @@ __global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__re
         dbs = warp_sum(dbs);
         const float bb = (dbs * mu - ds) * a * a * a * inv_c;
         const float cc = -bb * mu - dbs * a * inv_c;
-        float4 *dr = reinterpret_cast<float4 *>(dx + (size_t)row * C);
 #pragma unroll
         for (int i = 0; i < kNV; i++) {
             const int c = lane + 32 * i;
             if (c < nvec) {
-                float4 o = dr[c];  // accumulated, like the reference
+                float4 o = kEarly ? ov[kEarly ? i : 0] : dr[c];  // accumulated, like the reference
                 o.x += a * gv[i].x + bb * xv[i].x + cc, o.y += a * gv[i].y + bb * xv[i].y + cc;
                 o.z += a * gv[i].z + bb * xv[i].z + cc, o.w += a * gv[i].w + bb * xv[i].w + cc;
                 dr[c] = o;
             }
         }
     }
-    // block-level reduction of the column sums, then one atomic per column and block
+    // Column sums: over the warps of the block in shared memory, then over the kCluster blocks of the cluster
+    // through distributed shared memory, then one atomic per column and cluster.  (With one atomic per column
+    // and block, 444 blocks queued up on the same 1536 addresses and the kernel spent a third of its time
+    // waiting for them to drain.)
+    float4 *tot = red + kWarpsPerBlock * nvec;  // [2][nvec]: this block's sums for dW and db
     for (int pass = 0; pass < 2; pass++) {
-        float *dst = pass == 0 ? dw : db;
-        if (dst == nullptr) continue;  // uniform over the block
 #pragma unroll
         for (int i = 0; i < kNV; i++) {
             const int c = lane + 32 * i;
@@ -156,13 +169,29 @@ __global__ void __launch_bounds__(kThreads) ln_backward_kernel(const float *__re
                 const float4 u = red[k * nvec + c];
                 t.x += u.x, t.y += u.y, t.z += u.z, t.w += u.w;
             }
-            atomicAdd(dst + 4 * c, t.x);
-            atomicAdd(dst + 4 * c + 1, t.y);
-            atomicAdd(dst + 4 * c + 2, t.z);
-            atomicAdd(dst + 4 * c + 3, t.w);
+            tot[pass * nvec + c] = t;
         }
         __syncthreads();
     }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (cluster.block_rank() == 0) {
+        for (int c = threadIdx.x; c < 2 * nvec; c += kThreads) {
+            float *dst = c < nvec ? dw : db;
+            if (dst == nullptr) continue;
+            float4 t = tot[c];
+            for (unsigned r = 1; r < cluster.num_blocks(); r++) {
+                const float4 u = *cluster.map_shared_rank(tot + c, r);
+                t.x += u.x, t.y += u.y, t.z += u.z, t.w += u.w;
+            }
+            const int col = 4 * (c < nvec ? c : c - nvec);
+            atomicAdd(dst + col, t.x);
+            atomicAdd(dst + col + 1, t.y);
+            atomicAdd(dst + col + 2, t.z);
+            atomicAdd(dst + col + 3, t.w);
+        }
+    }
+    cluster.sync();  // the other blocks' shared memory stays alive until block 0 has read it
 }
 
 int grid_for(int rows, int blocks_per_sm) {
@@ -184,14 +213,30 @@ int launch_fwd(const float *x, const float *w, const float *b, float eps, float 
 template <int kNV>
 int launch_bwd(const float *dy, const float *x, const float *mean, const float *rstd, const float *w, float *dw, float *db,
                float *dx, int rows, int C, cudaStream_t s) {
-    const size_t smem = (size_t)kWarpsPerBlock * (C / 4) * sizeof(float4);
+    const size_t smem = (size_t)(kWarpsPerBlock + 2) * (C / 4) * sizeof(float4);
     auto kernel = ln_backward_kernel<kNV>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return (int)attn::launch_after_previous(kernel, dim3(grid_for(rows, 3)), dim3(kThreads), smem, s, dy, x, mean, rstd, w, dw,
-                                            db, dx, rows, C);
+    // clusters of kCluster blocks (the grid is a whole number of them; blocks without rows add zeros),
+    // launched as a programmatic dependent of the previous kernel like every kernel of the library
+    const int grid = (grid_for(rows, kNV <= 6 ? 4 : 3) + kCluster - 1) / kCluster * kCluster;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = kCluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, dy, x, mean, rstd, w, dw, db, dx, rows, C);
 }
 
 }  // namespace
