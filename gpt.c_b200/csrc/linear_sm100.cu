@@ -615,6 +615,18 @@ int pick_splits(int tiles, int kb_total, int sms) {
     return best;
 }
 
+// The same choice for dW, whose contraction (the rows of dy) is always cut: up to 32 pieces.
+int pick_splits_dw(int tiles, int kb_total, int sms, int overhead) {
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= 32 && s <= kb_total; s++) {
+        const long long rounds = ((long long)tiles * s + sms - 1) / sms;
+        const long long cost = rounds * ((kb_total + s - 1) / s + overhead);
+        if (best_cost < 0 || cost < best_cost) best = s, best_cost = cost;
+    }
+    return best;
+}
+
 bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
 
 }  // namespace
@@ -720,7 +732,9 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
         // result past N are dropped by the copy engine)
         const int bn = K % 256 == 0 ? 256 : (K % 192 == 0 ? 192 : 128);
         const int tiles = ((N + kBM - 1) / kBM) * ((K + bn - 1) / bn);
-        const int splits = (2 * sms + tiles - 1) / tiles;  // about two work items per SM
+        // pieces of the contraction: whole rounds over the SMs cost (steps per piece + a fixed charge for the
+        // piece's epilogue and reduction) each; e.g. QKV: 54 tiles, 256 steps -> 5 pieces in 2 rounds of 52 steps
+        const int splits = pick_splits_dw(tiles, (M + kBK - 1) / kBK, sms, 8);
         Problem pdw = make_problem(N, K, M, bn, splits);
         pdw.a_one = map_mn_major_blocks(&ma, g, M, np, 4) == 0;
         if (!pdw.a_one && (rc = map_mn_major(&ma, g, M, np)) != 0) return rc;
