@@ -2,12 +2,15 @@
 reference uses for the same layers (cuBLAS in TF32 tensor-op math, here through torch.addmm /
 torch.matmul with TF32 allowed), for the Linear shapes of GPT-2 124M at B=8, T=1024.
 
-    python gpt.c_b200/bench_linear.py [--steps 30] [--cold]
+    python gpt.c_b200/bench_linear.py [--steps 30] [--cold] [--shape M,N,K] [--only fwd]
 
 Prints one JSON line per shape: microseconds and algorithmic TFLOP/s (2*M*N*K per product) of
 forward (with and without the fused bf16 planes), backward (dx + dW + db) and its two products
 alone, next to the cuBLAS time of the same product.  Inputs stay resident; --cold writes a 512 MB
 buffer between launches so that every launch starts with a cold L2 (default: warm, back to back).
+--shape times one other shape instead (e.g. 8192,50257,768, the vocabulary projection; the planes
+variant is skipped when N is not a multiple of 8); --only fwd launches nothing but the forward kernel
+(for a profiler capture).
 """
 from __future__ import annotations
 
@@ -37,6 +40,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cold", action="store_true")
+    ap.add_argument("--shape", default=None, metavar="M,N,K")
+    ap.add_argument("--only", default=None, choices=["fwd"])
     args = ap.parse_args()
 
     pkg = entry.load_package()
@@ -68,15 +73,24 @@ def main() -> None:
                 total += a.elapsed_time(b)
         return total / args.steps * 1e3  # microseconds
 
-    for name, M, N, K in SHAPES:
+    shapes = SHAPES
+    if args.shape:
+        m, n, k = (int(v) for v in args.shape.split(","))
+        shapes = [("custom", m, n, k)]
+    for name, M, N, K in shapes:
         x = torch.randn(M, K, device="cuda")
         w = torch.randn(N, K, device="cuda") * 0.05
         b = torch.randn(N, device="cuda")
         dy = torch.randn(M, N, device="cuda")
         dw = torch.zeros(N, K, device="cuda")
         db = torch.zeros(N, device="cuda")
-        planes = torch.empty(4 * M * N + 512, device="cuda", dtype=torch.uint8)
         fl = 2.0 * M * N * K
+        if args.only == "fwd":
+            us = {"fwd": timed(lambda: pkg.linear_forward(x, w, b))}
+            print(json.dumps({"layer": name, "M": M, "N": N, "K": K, "us": {"fwd": round(us["fwd"], 1)},
+                              "tflops": {"fwd": round(fl / us["fwd"] / 1e6, 1)}, "status": pkg.device_status()}), flush=True)
+            continue
+        planes = torch.empty(4 * M * N + 512, device="cuda", dtype=torch.uint8) if N % 8 == 0 else None
 
         def cublas_bwd():
             _ = dy @ w
@@ -85,7 +99,7 @@ def main() -> None:
 
         us = {
             "fwd": timed(lambda: pkg.linear_forward(x, w, b)),
-            "fwd_with_planes": timed(lambda: pkg.linear_forward(x, w, b, planes=planes)),
+            "fwd_with_planes": timed(lambda: pkg.linear_forward(x, w, b, planes=planes)) if planes is not None else None,
             "fwd_cublas_tf32": timed(lambda: torch.addmm(b, x, w.t())),
             "bwd": timed(lambda: pkg.linear_backward(dy, x, w, dw, db)),
             "bwd_cublas_tf32": timed(cublas_bwd),
@@ -98,8 +112,9 @@ def main() -> None:
         if status != 0:
             raise SystemExit(f"kernel status word {status}")
         line = {"layer": name, "M": M, "N": N, "K": K, "l2": "cold" if args.cold else "warm",
-                "us": {k: round(v, 1) for k, v in us.items()},
-                "tflops": {k: round((fl if k.startswith(("fwd", "dx", "dw")) else 2 * fl) / v / 1e6, 1) for k, v in us.items()}}
+                "us": {k: round(v, 1) for k, v in us.items() if v is not None},
+                "tflops": {k: round((fl if k.startswith(("fwd", "dx", "dw")) else 2 * fl) / v / 1e6, 1)
+                           for k, v in us.items() if v is not None}}
         print(json.dumps(line), flush=True)
 
 
