@@ -27,6 +27,7 @@ SHAPES = [
     (70, 95, 64),                  # 31 of 32 columns in the last block: the padded copy of dy reads its last word alone
     (70, 94, 32),                  # rows of dy start 0 or 2 floats past a 16-byte boundary
     (9, 16415, 32),                # long contraction for dx (513 steps): cut into pieces that add into a zeroed dx
+    (260, 16392, 768),             # weight above 48 MB with 16-byte-aligned rows of y: row-fastest tile order, copy-engine stores
 ]
 
 
