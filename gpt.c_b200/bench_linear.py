@@ -2,14 +2,14 @@
 reference uses for the same layers (cuBLAS in TF32 tensor-op math, here through torch.addmm /
 torch.matmul with TF32 allowed), for the Linear shapes of GPT-2 124M at B=8, T=1024.
 
-    python gpt.c_b200/bench_linear.py [--steps 30] [--cold] [--shape M,N,K] [--only fwd]
+    python gpt.c_b200/bench_linear.py [--steps 30] [--cold] [--shape M,N,K] [--only fwd|dx|dw]
 
 Prints one JSON line per shape: microseconds and algorithmic TFLOP/s (2*M*N*K per product) of
 forward (with and without the fused bf16 planes), backward (dx + dW + db) and its two products
 alone, next to the cuBLAS time of the same product.  Inputs stay resident; --cold writes a 512 MB
 buffer between launches so that every launch starts with a cold L2 (default: warm, back to back).
 --shape times one other shape instead (e.g. 8192,50257,768, the vocabulary projection; the planes
-variant is skipped when N is not a multiple of 8); --only fwd launches nothing but the forward kernel
+variant is skipped when N is not a multiple of 8); --only fwd|dx|dw launches nothing but that product
 (for a profiler capture).
 """
 from __future__ import annotations
@@ -41,7 +41,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--cold", action="store_true")
     ap.add_argument("--shape", default=None, metavar="M,N,K")
-    ap.add_argument("--only", default=None, choices=["fwd"])
+    ap.add_argument("--only", default=None, choices=["fwd", "dx", "dw"])
     args = ap.parse_args()
 
     pkg = entry.load_package()
@@ -85,10 +85,13 @@ def main() -> None:
         dw = torch.zeros(N, K, device="cuda")
         db = torch.zeros(N, device="cuda")
         fl = 2.0 * M * N * K
-        if args.only == "fwd":
-            us = {"fwd": timed(lambda: pkg.linear_forward(x, w, b))}
-            print(json.dumps({"layer": name, "M": M, "N": N, "K": K, "us": {"fwd": round(us["fwd"], 1)},
-                              "tflops": {"fwd": round(fl / us["fwd"] / 1e6, 1)}, "status": pkg.device_status()}), flush=True)
+        if args.only:
+            one = {"fwd": lambda: pkg.linear_forward(x, w, b),
+                   "dx": lambda: pkg.linear_backward(dy, x, w, None, None),
+                   "dw": lambda: pkg.linear_backward(dy, x, w, dw, None, want_dx=False)}[args.only]
+            t_us = timed(one)
+            print(json.dumps({"layer": name, "M": M, "N": N, "K": K, "us": {args.only: round(t_us, 1)},
+                              "tflops": {args.only: round(fl / t_us / 1e6, 1)}, "status": pkg.device_status()}), flush=True)
             continue
         planes = torch.empty(4 * M * N + 512, device="cuda", dtype=torch.uint8) if N % 8 == 0 else None
 
