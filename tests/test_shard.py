@@ -77,3 +77,21 @@ def test_two_rank_gloo_shards_reassemble(tmp_path, oracle):
     port = 29500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert open(tmp_path / "ok").read() == "1"
+
+
+def test_bench_cpu_binding_is_harmless_without_nvml():
+    """bench.py binds a rank to the cores NVML lists for its GPU; without a GPU (or NVML) it must return
+    None and leave the process's affinity alone."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    before = os.sched_getaffinity(0)
+    got = bench.bind_to_gpu_cpus(0)
+    after = os.sched_getaffinity(0)
+    if torch.cuda.is_available():
+        assert got is None or (isinstance(got, int) and got == len(after) and after <= before)
+        os.sched_setaffinity(0, before)
+    else:
+        assert got is None and after == before
