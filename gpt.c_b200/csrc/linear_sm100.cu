@@ -46,9 +46,11 @@ template <int kBN, int kStages, bool kPlanes>
 struct __align__(1024) SmemT {
     uint8_t a[kStages][kATileBytes];
     uint8_t b[kStages][kBN * kBK * 4];
-    // 64 output columns of a tile on their way out: fp32 columns 0-31, fp32 columns 32-63 and, when the
-    // bf16 planes are wanted, hi plane (64 columns), lo plane; each [128 rows x 128 bytes], swizzled
-    uint8_t out[kPlanes ? 4 : 2][16384];
+    // 64 output columns of a tile on their way out: fp32 columns 0-31 and fp32 columns 32-63; when the bf16
+    // planes are wanted, the same two buffers then carry the hi plane (64 columns) and the lo plane of the
+    // chunk (a second round through the copy engine: two more buffers would cost a pipeline stage, and the
+    // depth of the operand pipeline is what bounds this kernel); each [128 rows x 128 bytes], swizzled
+    uint8_t out[2][16384];
     uint64_t full[kStages], empty[kStages];
     uint64_t acc_full[2], acc_empty[2];
     uint64_t out_ready, out_free;
@@ -247,6 +249,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int row = (quarter << 5) | lane;
         const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
         int j = 0, chunk_count = 0;
+        int sub = 0;  // stagings handed to the copy engine so far (one per chunk, two with the planes)
         bool ok = true;
         for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x, j++) {
             const Work wk = decode(p, w);
@@ -294,8 +297,8 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         lp[e] = *reinterpret_cast<const uint32_t *>(&ll);
                     }
                 }
-                // the copy engine must have read the previous chunk out of the staging tile
-                if (chunk_count >= 1 && !mbar_wait_warp(&sm.out_free, (chunk_count - 1) & 1, ctx, SITE_OUT_FREE)) {
+                // the copy engine must have read the previous staging out of the two buffers
+                if (sub >= 1 && !mbar_wait_warp(&sm.out_free, (sub - 1) & 1, ctx, SITE_OUT_FREE)) {
                     ok = false;
                     break;
                 }
@@ -304,21 +307,11 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     uint8_t *dst = sm.out[half] + row * 128 + ((q ^ (row & 7)) << 4);
                     *reinterpret_cast<uint4 *>(dst) = make_uint4(R(4 * q), R(4 * q + 1), R(4 * q + 2), R(4 * q + 3));
                 }
-                if (kEpi == 0 && kPlanes) {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {  // bf16 planes: this half's 32 columns = 4 chunks of 8 values
-                        const int off = row * 128 + (((4 * half + q) ^ (row & 7)) << 4);
-                        *reinterpret_cast<uint4 *>(sm.out[kPlanes ? 2 : 0] + off) =
-                            make_uint4(hp[4 * q], hp[4 * q + 1], hp[4 * q + 2], hp[4 * q + 3]);
-                        *reinterpret_cast<uint4 *>(sm.out[kPlanes ? 3 : 0] + off) =
-                            make_uint4(lp[4 * q], lp[4 * q + 1], lp[4 * q + 2], lp[4 * q + 3]);
-                    }
-                }
 #undef R
                 if (kDirect) {
                     // every row of the staged chunk is written by one warp instruction: 32 consecutive floats
                     mbar_arrive(&sm.out_ready);
-                    if (!mbar_wait_warp(&sm.out_ready, chunk_count & 1, ctx, SITE_OUT_READY)) {
+                    if (!mbar_wait_warp(&sm.out_ready, sub & 1, ctx, SITE_OUT_READY)) {
                         ok = false;
                         break;
                     }
@@ -333,31 +326,60 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         if (wk.m0 + rr < p.M && cbase + cc < p.N) c_direct[(size_t)(wk.m0 + rr) * p.N + cbase + cc] = v;
                     }
                     mbar_arrive(&sm.out_free);
+                    sub++;
                 } else {
                     fence_proxy_async_smem();
                     mbar_arrive(&sm.out_ready);
+                    sub++;
+                    if (kEpi == 0 && kPlanes) {
+                        // second round: once the fp32 tiles have been read, the same buffers take the planes
+                        if (!mbar_wait_warp(&sm.out_free, (sub - 1) & 1, ctx, SITE_OUT_FREE)) {
+                            ok = false;
+                            break;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {  // this half's 32 columns = 4 chunks of 8 bf16 values
+                            const int off = row * 128 + (((4 * half + q) ^ (row & 7)) << 4);
+                            *reinterpret_cast<uint4 *>(sm.out[0] + off) =
+                                make_uint4(hp[4 * q], hp[4 * q + 1], hp[4 * q + 2], hp[4 * q + 3]);
+                            *reinterpret_cast<uint4 *>(sm.out[1] + off) =
+                                make_uint4(lp[4 * q], lp[4 * q + 1], lp[4 * q + 2], lp[4 * q + 3]);
+                        }
+                        fence_proxy_async_smem();
+                        mbar_arrive(&sm.out_ready);
+                        sub++;
+                    }
                 }
             }
         }
     } else if (warp == 3 && !kDirect) {
         // ------------------------------ output copies ------------------------------
         if (lane == 0) {
-            int chunk_count = 0;
+            int sub = 0;
             bool ok = true;
             for (int w = blockIdx.x; ok && w < p.total; w += gridDim.x) {
                 const Work wk = decode(p, w);
-                for (int c = 0; c < kBN / 64; c++, chunk_count++) {
+                for (int c = 0; c < kBN / 64; c++) {
                     const int col0 = wk.n0 + 64 * c;
-                    if (!mbar_wait(&sm.out_ready, chunk_count & 1, ctx, SITE_OUT_READY)) {
+                    if (!mbar_wait(&sm.out_ready, sub & 1, ctx, SITE_OUT_READY)) {
                         ok = false;
                         break;
                     }
+                    sub++;
                     if (kEpi == 0) {
                         tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
                         tma_store_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
-                        if (kPlanes) {
-                            tma_store_3d(sm.out[kPlanes ? 2 : 0], &map_planes, col0, wk.m0, 0);
-                            tma_store_3d(sm.out[kPlanes ? 3 : 0], &map_planes, col0, wk.m0, 1);
+                        if (kPlanes) {  // second round through the same buffers: hi plane, lo plane
+                            bulk_commit();
+                            bulk_wait_read_all();
+                            mbar_arrive(&sm.out_free);
+                            if (!mbar_wait(&sm.out_ready, sub & 1, ctx, SITE_OUT_READY)) {
+                                ok = false;
+                                break;
+                            }
+                            sub++;
+                            tma_store_3d(sm.out[0], &map_planes, col0, wk.m0, 0);
+                            tma_store_3d(sm.out[1], &map_planes, col0, wk.m0, 1);
                         }
                     } else {
                         tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
@@ -581,14 +603,14 @@ template <bool kAMN, bool kBMN, int kEpi>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const CUtensorMap &mp, const float *bias,
            bool planes, const Problem &p, int *status, cudaStream_t s) {
     if (p.bn == 256) {
-        if (planes) return launch_one<kAMN, kBMN, kEpi, 256, 3, true>(ma, mb, mc, mp, bias, p, status, s);
+        if (planes) return launch_one<kAMN, kBMN, kEpi, 256, 4, true>(ma, mb, mc, mp, bias, p, status, s);
         return launch_one<kAMN, kBMN, kEpi, 256, 4, false>(ma, mb, mc, mp, bias, p, status, s);
     }
     if (p.bn == 192) {
         if (planes) return launch_one<kAMN, kBMN, kEpi, 192, 4, true>(ma, mb, mc, mp, bias, p, status, s);
         return launch_one<kAMN, kBMN, kEpi, 192, 4, false>(ma, mb, mc, mp, bias, p, status, s);
     }
-    if (planes) return launch_one<kAMN, kBMN, kEpi, 128, 5, true>(ma, mb, mc, mp, bias, p, status, s);
+    if (planes) return launch_one<kAMN, kBMN, kEpi, 128, 6, true>(ma, mb, mc, mp, bias, p, status, s);
     return launch_one<kAMN, kBMN, kEpi, 128, 6, false>(ma, mb, mc, mp, bias, p, status, s);
 }
 
