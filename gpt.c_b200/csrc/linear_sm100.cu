@@ -50,7 +50,9 @@ struct __align__(1024) SmemT {
     // planes are wanted, the same two buffers then carry the hi plane (64 columns) and the lo plane of the
     // chunk (a second round through the copy engine: two more buffers would cost a pipeline stage, and the
     // depth of the operand pipeline is what bounds this kernel); each [128 rows x 128 bytes], swizzled
-    uint8_t out[2][16384];
+    // 192-wide tiles without planes stage through ONE buffer (32 columns per round): that leaves room for a
+    // fifth pipeline stage of 40 KB
+    uint8_t out[(kBN == 192 && !kPlanes) ? 1 : 2][16384];
     uint64_t full[kStages], empty[kStages];
     uint64_t acc_full[2], acc_empty[2];
     uint64_t out_ready, out_free;
@@ -132,6 +134,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     using Smem = SmemT<kBN, kStages, kPlanes>;
     constexpr uint32_t kTmemCols = 2 * kBN <= 256 ? 256 : 512;  // a power of two that holds two accumulators
     constexpr int kBTileBytes = kBN * kBK * 4;
+    constexpr bool kOut1 = kBN == 192 && !kPlanes;  // one output staging buffer (see SmemT)
     Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_SMEM_ALIGN);
@@ -297,6 +300,28 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         lp[e] = *reinterpret_cast<const uint32_t *>(&ll);
                     }
                 }
+                if (kOut1) {
+                    // one staging buffer: the two column halves of the chunk go through it one after the other
+#pragma unroll 1
+                    for (int hsel = 0; hsel < 2; hsel++) {
+                        if (sub >= 1 && !mbar_wait_warp(&sm.out_free, (sub - 1) & 1, ctx, SITE_OUT_FREE)) {
+                            ok = false;
+                            break;
+                        }
+                        if (half == hsel) {
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                uint8_t *dst = sm.out[0] + row * 128 + ((q ^ (row & 7)) << 4);
+                                *reinterpret_cast<uint4 *>(dst) = make_uint4(R(4 * q), R(4 * q + 1), R(4 * q + 2), R(4 * q + 3));
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        mbar_arrive(&sm.out_ready);
+                        sub++;
+                    }
+                    if (!ok) break;
+                    continue;
+                }
                 // the copy engine must have read the previous staging out of the two buffers
                 if (sub >= 1 && !mbar_wait_warp(&sm.out_free, (sub - 1) & 1, ctx, SITE_OUT_FREE)) {
                     ok = false;
@@ -304,7 +329,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 }
 #pragma unroll
                 for (int q = 0; q < 8; q++) {  // fp32: this half's box of 32 columns, 8 chunks of 16 bytes per row
-                    uint8_t *dst = sm.out[half] + row * 128 + ((q ^ (row & 7)) << 4);
+                    uint8_t *dst = sm.out[kOut1 ? 0 : half] + row * 128 + ((q ^ (row & 7)) << 4);
                     *reinterpret_cast<uint4 *>(dst) = make_uint4(R(4 * q), R(4 * q + 1), R(4 * q + 2), R(4 * q + 3));
                 }
 #undef R
@@ -321,7 +346,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     for (int k = 0; k < (128 * 64) / kEpiThreads; k++) {
                         const int e = et + kEpiThreads * k;
                         const int rr = e >> 6, cc = e & 63;
-                        const float v = *reinterpret_cast<const float *>(sm.out[cc >> 5] + rr * 128 +
+                        const float v = *reinterpret_cast<const float *>(sm.out[kOut1 ? 0 : (cc >> 5)] + rr * 128 +
                                                                          ((((cc & 31) >> 2) ^ (rr & 7)) << 4) + ((cc & 3) << 2));
                         if (wk.m0 + rr < p.M && cbase + cc < p.N) c_direct[(size_t)(wk.m0 + rr) * p.N + cbase + cc] = v;
                     }
@@ -342,7 +367,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             const int off = row * 128 + (((4 * half + q) ^ (row & 7)) << 4);
                             *reinterpret_cast<uint4 *>(sm.out[0] + off) =
                                 make_uint4(hp[4 * q], hp[4 * q + 1], hp[4 * q + 2], hp[4 * q + 3]);
-                            *reinterpret_cast<uint4 *>(sm.out[1] + off) =
+                            *reinterpret_cast<uint4 *>(sm.out[kOut1 ? 0 : 1] + off) =
                                 make_uint4(lp[4 * q], lp[4 * q + 1], lp[4 * q + 2], lp[4 * q + 3]);
                         }
                         fence_proxy_async_smem();
@@ -366,9 +391,22 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         break;
                     }
                     sub++;
-                    if (kEpi == 0) {
+                    if (kOut1) {  // one buffer, two rounds of 32 columns
+                        if (kEpi == 0) tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                        else tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
+                        bulk_commit();
+                        bulk_wait_read_all();
+                        mbar_arrive(&sm.out_free);
+                        if (!mbar_wait(&sm.out_ready, sub & 1, ctx, SITE_OUT_READY)) {
+                            ok = false;
+                            break;
+                        }
+                        sub++;
+                        if (kEpi == 0) tma_store_3d(sm.out[0], &map_c, col0 + 32, wk.m0, 0);
+                        else tma_reduce_add_3d(sm.out[0], &map_c, col0 + 32, wk.m0, 0);
+                    } else if (kEpi == 0) {
                         tma_store_3d(sm.out[0], &map_c, col0, wk.m0, 0);
-                        tma_store_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                        tma_store_3d(sm.out[kOut1 ? 0 : 1], &map_c, col0 + 32, wk.m0, 0);
                         if (kPlanes) {  // second round through the same buffers: hi plane, lo plane
                             bulk_commit();
                             bulk_wait_read_all();
@@ -379,11 +417,11 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             }
                             sub++;
                             tma_store_3d(sm.out[0], &map_planes, col0, wk.m0, 0);
-                            tma_store_3d(sm.out[1], &map_planes, col0, wk.m0, 1);
+                            tma_store_3d(sm.out[kOut1 ? 0 : 1], &map_planes, col0, wk.m0, 1);
                         }
                     } else {
                         tma_reduce_add_3d(sm.out[0], &map_c, col0, wk.m0, 0);
-                        tma_reduce_add_3d(sm.out[1], &map_c, col0 + 32, wk.m0, 0);
+                        tma_reduce_add_3d(sm.out[kOut1 ? 0 : 1], &map_c, col0 + 32, wk.m0, 0);
                     }
                     bulk_commit();
                     bulk_wait_read_all();
@@ -608,7 +646,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, 
     }
     if (p.bn == 192) {
         if (planes) return launch_one<kAMN, kBMN, kEpi, 192, 4, true>(ma, mb, mc, mp, bias, p, status, s);
-        return launch_one<kAMN, kBMN, kEpi, 192, 4, false>(ma, mb, mc, mp, bias, p, status, s);
+        return launch_one<kAMN, kBMN, kEpi, 192, 5, false>(ma, mb, mc, mp, bias, p, status, s);
     }
     if (planes) return launch_one<kAMN, kBMN, kEpi, 128, 6, true>(ma, mb, mc, mp, bias, p, status, s);
     return launch_one<kAMN, kBMN, kEpi, 128, 6, false>(ma, mb, mc, mp, bias, p, status, s);
