@@ -17,6 +17,7 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
     bool ready = false;
     int *status = nullptr;  // device word written by kernels whose bounded waits run out
+    int num_sms = 0;        // the persistent backward kernel runs one CTA per SM
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -148,6 +149,9 @@ int attn_sm100_init(void) {
     if ((e = attn::fast_fwd_set_attributes()) != cudaSuccess) return (int)e;
     if ((e = attn::fast_bwd_set_attributes()) != cudaSuccess) return (int)e;
 
+    int sms = 0;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    g_dev[dev].num_sms = sms;
     int *st = nullptr;
     if ((e = cudaMalloc(&st, sizeof(int))) != cudaSuccess) return (int)e;
     if ((e = cudaMemset(st, 0, sizeof(int))) != cudaSuccess) return (int)e;
@@ -245,7 +249,7 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
         if (rc != 0) return rc;
         rc = encode_rows_f32(&map_dx, dqkv, B, T, 3 * H * D);
         if (rc != 0) return rc;
-        e = attn::launch_fast_backward(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, ds->status, s);
+        e = attn::launch_fast_backward(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, ds->num_sms, ds->status, s);
     } else {
         if (prepare) {
             e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, B, T, H, D, s);

@@ -5,18 +5,32 @@
 // permute-accumulate become one kernel that recomputes the probabilities from the saved
 // log-sum-exp and never writes a T x T matrix.
 //
-// One CTA owns one (batch, head) and one tile of 128 keys (K_j, V_j stay in shared memory) and
-// walks the query tiles i = j .. last.  Everything is computed transposed so that the key index
-// is the tensor-memory lane:
+// The kernel is persistent: one CTA per SM walks a list of work items.  A work item is one (batch,
+// head) and one tile of 128 keys (K_j, V_j stay in shared memory) together with the query tiles
+// i = j .. last.  Items are ordered heaviest first (key tile 0 sees every query tile) and dealt to
+// the CTAs in a snake (round r goes left to right when r is even, right to left when it is odd),
+// which balances the SMs as well as a greedy longest-first assignment does without any counter in
+// global memory.  Barriers, tensor memory and the Q/dO ring live for the whole launch; the K/V
+// tiles of the next item are requested as soon as the last tensor-core instruction that reads the
+// current ones has completed, so that set-up of item w+1 overlaps the drain of item w.
+//
+// Everything is computed transposed so that the key index is the tensor-memory lane:
 //     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (B = Q / dO half, K-major)
 //     P^T  = exp2(S^T * c - lse_i)        dS^T = P^T * (dP^T - delta_i)      (one thread per key)
 //     dV_j += P^T dO_i            dK_j += dS^T Q_i                  (A from tensor memory)
 //     dQ_i  = dS K_j                                                (A = dS^T tile in shared
 //                                                                    memory read MN-major)
-// dK_j and dV_j accumulate in tensor memory over the whole loop and leave once through bulk
-// tensor stores; dQ_i is staged as an fp32 tile in shared memory and added into the (zeroed) dq
-// third of the output by bulk tensor reductions, since other key tiles contribute to the same
-// rows.  Every product is hi*hi + hi*lo + lo*hi on bf16 pairs.
+// dK_j and dV_j accumulate in tensor memory over the whole item and leave once, staged in shared
+// memory, through bulk tensor stores.  dQ_i leaves after every query tile: staged as fp32 in the
+// dS^T buffer (the only 32 KiB that are ever free: the dQ product that read it has completed) and
+// added into the (zeroed) dq third of the output by bulk tensor reductions, since other key tiles
+// contribute to the same rows.  The copy engine takes ~2600 cycles to drain a tile of reductions
+// and the next dS^T has to wait for that; the variants that were measured against this one all
+// lost: staging half or all of the tile in the V hi plane (dead once it is in tensor memory),
+// flushing after half B instead of after half A, and adding dQ from registers with red.global (one
+// thread per row, or four lanes per row after a 16x256b tensor-memory load: the reductions back up
+// into the compute warps, ~1900 cycles per tile).  Every product is hi*hi + hi*lo + lo*hi on bf16
+// pairs.
 //
 // Each query tile is processed as two halves of 64 queries (A, B) with their own barriers, so the
 // tensor cores and the compute warps overlap: while the compute warps turn S^T/dP^T of half B
@@ -24,11 +38,13 @@
 // next tile's scores.
 //
 // Warp roles (640 threads):
-//   warp 0      TMA producer: K, V once; Q/dO half tiles through a ring of three slots
+//   warp 0      TMA producer: K, V of every item; Q/dO half tiles through a ring of three slots that
+//               runs on across items
 //   warp 1      issues the score MMAs (S^T, dP^T), in order
 //   warp 2      allocates tensor memory; stages the row statistics (-lse, -delta) of every query
-//               tile; drives the output copies (dQ reductions, final dK / dV stores)
-//   warp 3      issues the gradient MMAs (dV, dK per half; dQ per tile), whichever is ready first
+//               tile, two tiles ahead; drives the output copies (dQ reductions, dK / dV stores)
+//   warp 3      issues the gradient MMAs in the order they become ready: dV, dK of half A, of
+//               half B, then dQ of the tile
 //   warps 4-19  compute.  A compute warp's quarter (warp % 4) selects the 32 tensor-memory lanes
 //               it may touch (keys for S^T / dP^T / dK / dV, queries for dQ); its column group
 //               (0..3) selects 16 of the 64 query columns of a half and 16 of the 64 columns of
@@ -36,11 +52,13 @@
 // Two issuing warps on two schedulers, each electing its issuing lane once: a single issuing warp
 // competes with four busy compute warps for its scheduler's issue slots and feeds the tensor pipe
 // at well under its rate.  Dependencies between the two (a score task overwrites the columns a
-// gradient task read) go through completion barriers, not through issue order.
+// gradient task read) go through completion barriers, not through issue order.  Every role blocks
+// on the one barrier its next task needs (the order in which tasks become ready is fixed), so idle
+// roles sleep in mbarrier.try_wait instead of polling.
 //
 // Tensor memory: S^T [0,128)  dP^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448)
-// K hi [448,480)  V hi [480,512).  The hi planes of K and V are copied there once so that two of
-// the three terms of S^T and dP^T take their A operand from tensor memory: an MMA with both
+// K hi [448,480)  V hi [480,512).  The hi planes of K and V are copied there once per item so that
+// two of the three terms of S^T and dP^T take their A operand from tensor memory: an MMA with both
 // operands in shared memory is limited by shared-memory bandwidth (48 instead of 32 cycles at
 // N = 64).  P^T and dS^T overwrite S^T and dP^T in place: each run of 16 columns becomes 8 columns
 // of packed bf16 hi parts followed by 8 columns of packed lo parts.
@@ -73,50 +91,57 @@ struct __align__(1024) BwdSmem {
     uint8_t ds[2][2][kPlaneTile];
     float lse2[2][kTile];          // -log-sum-exp of the query tile in log2 units, double buffered
     float delta[2][kTile];         // -rowsum(dO * O)
-    uint64_t kv_full;
+    // one completion per work item
+    uint64_t kv_full;     // K_j, V_j have landed in shared memory
+    uint64_t kv_tmem;     // their hi planes have been copied to tensor memory
+    uint64_t v_free;      // the item's last dP^T product has completed: V_j may be overwritten
+    uint64_t k_free;      // the item's last dQ product has completed: K_j may be overwritten
+    uint64_t grads_done;  // the item's last dV / dK product has completed
+    uint64_t kv_out_full; // the item's dK / dV tiles are staged in two slots of the (then dead) Q/dO ring
+    uint64_t stage_free;  // ... and the copy engine has read them
+    // one completion per query tile: its dQ tile is staged / the copy engine has read it.  (Every waiter
+    // sees every phase of the barriers it waits on: a parity wait cannot tell "the phase before mine is
+    // still open" from "mine has completed".)
+    uint64_t out_full, out_free;
+    // one completion per half tile (ring) or per query tile
     uint64_t in_full[kSlots], in_empty[kSlots];
-    uint64_t st_full[2], pds_full[2];                       // [half]
-    uint64_t ds_full;                                       // dS^T of both halves is in shared memory
-    uint64_t dq_full[2];                                    // [iteration parity]
-    uint64_t out_full, out_free;                            // staged dQ tile: written / read by the copy engine
-    uint64_t kv_out_full;                                   // staged dK / dV tiles written
-    uint64_t stats_full[2], stats_free[2], kv_tmem;  // [statistics buffer]
+    uint64_t st_full[2], pds_full[2];  // [half]
+    uint64_t ds_full;                  // dS^T of both halves is in shared memory
+    uint64_t dq_full[2];               // [tile parity]
+    uint64_t stats_full[2], stats_free[2];  // [statistics buffer]
     uint32_t tmem_base;
     int abort_flag;
 };
 
 enum Site : int {
     SITE_IN_EMPTY = 101, SITE_IN_FULL, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
-    SITE_MMA_IDLE, SITE_STATS_FREE, SITE_KV_TMEM, SITE_OUT_FULL, SITE_OUT_FREE, SITE_SMEM_ALIGN
+    SITE_PDS_FULL, SITE_STATS_FREE, SITE_KV_TMEM, SITE_DS_FULL, SITE_GRADS_DONE, SITE_SMEM_ALIGN, SITE_V_FREE, SITE_K_FREE,
+    SITE_KV_OUT_FULL, SITE_STAGE_FREE, SITE_TMEM_BASE, SITE_OUT_FULL, SITE_OUT_FREE
 };
 
-// Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
-#ifdef ATTN_TRACE
-__device__ long long g_bwd_trace[2 * 16 * 8];
-#define BWD_TRACE(cond, role, it, k)                                                              \
-    do {                                                                                          \
-        if (blockIdx.x == 0 && (cond)) g_bwd_trace[((role) * 16 + (it)) * 8 + (k)] = clock64();  \
-    } while (0)
-// life time of every 48th CTA in ns: rows 8..15 of role 1 are reused: [cta / 48][0..2]
-__device__ long long g_bwd_life[16 * 4];
-__device__ long long g_bwd_epi[8];
-#define BWD_EPI(k) do { if (blockIdx.x == 0 && threadIdx.x == 128) g_bwd_epi[k] = (long long)global_timer_ns(); } while (0)
-#define BWD_EPI2(k) do { if (blockIdx.x == 0) g_bwd_epi[k] = (long long)global_timer_ns(); } while (0)
-#define BWD_LIFE(k)                                                                          \
-    do {                                                                                     \
-        if (threadIdx.x == 128 && blockIdx.x % 48 == 0)                                      \
-            g_bwd_life[(blockIdx.x / 48) * 4 + (k)] = (long long)global_timer_ns();          \
-    } while (0)
-#else
-#define BWD_EPI(k) do {} while (0)
-#define BWD_EPI2(k) do {} while (0)
-#define BWD_LIFE(k) \
-    do {            \
-    } while (0)
-#define BWD_TRACE(cond, role, it, k) \
-    do {                             \
-    } while (0)
-#endif
+// Work list of one CTA.  Item p (0 = heaviest) is key tile p / BH of (batch, head) p % BH; round r of
+// the deal gives CTA c item r * G + c when r is even and r * G + (G - 1 - c) when it is odd.  Every
+// role of the CTA walks the same list with its own copy of this iterator.
+struct Work {
+    int jt, bh, niter;
+};
+struct WorkList {
+    int grid, cta, nitems, BH, nt, round;
+    __device__ WorkList(int BH_, int nt_) : grid((int)gridDim.x), cta((int)blockIdx.x), nitems(BH_ * nt_), BH(BH_), nt(nt_), round(0) {}
+    __device__ bool next(Work &w) {
+        while (round * grid < nitems) {
+            const int r = round++;
+            const int p = r * grid + ((r & 1) ? grid - 1 - cta : cta);
+            if (p < nitems) {
+                w.jt = p / BH;
+                w.bh = p - w.jt * BH;
+                w.niter = nt - w.jt;  // query tiles jt .. nt-1
+                return true;
+            }
+        }
+        return false;
+    }
+};
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -171,8 +196,8 @@ __device__ __forceinline__ void store_ds(uint8_t *tile_h, uint8_t *tile_l, int r
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_do,
-                const __grid_constant__ CUtensorMap map_dx, const float *__restrict__ lse, const float *__restrict__ delta, float *__restrict__ dqkv, int B, int T,
-                int H, float scale, float scale_log2, int *status) {
+                const __grid_constant__ CUtensorMap map_dx, const float *__restrict__ lse, const float *__restrict__ delta,
+                float *__restrict__ dqkv, int B, int T, int H, float scale, float scale_log2, int *status) {
     // The structure fills the whole 227 KiB, so there is no room to round the base up: the
     // swizzled tiles need 1024-byte alignment and the kernel refuses to run without it.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -185,61 +210,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = B * H;
     const int nt = (T + kTile - 1) / kTile;
-    const int jt = (int)(blockIdx.x / BH);  // key tile; tile 0 has the most work and goes first
-    const int bh = (int)(blockIdx.x % BH);
-    const int b = bh / H, h = bh % H;
     const int C = H * kD;
-    const int niter = nt - jt;  // query tiles jt .. nt-1
 
     WaitCtx ctx{&sm.abort_flag, status};
     pdl_launch_dependents();
-    BWD_LIFE(0);
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
         mbar_init(&sm.kv_full, 1);
+        mbar_init(&sm.kv_tmem, kComputeThreads);
+        mbar_init(&sm.v_free, 1);
+        mbar_init(&sm.k_free, 1);
+        mbar_init(&sm.grads_done, 1);
+        mbar_init(&sm.kv_out_full, kComputeThreads);
+        mbar_init(&sm.stage_free, 1);
+        mbar_init(&sm.out_full, kComputeThreads);
+        mbar_init(&sm.out_free, 1);
         for (int i = 0; i < 2; i++) {
             mbar_init(&sm.st_full[i], 1);
             mbar_init(&sm.pds_full[i], kComputeThreads);
             mbar_init(&sm.dq_full[i], 1);
+            mbar_init(&sm.stats_full[i], 32);
+            mbar_init(&sm.stats_free[i], kComputeThreads / 32);
         }
         for (int i = 0; i < kSlots; i++) {
             mbar_init(&sm.in_full[i], 1);
             mbar_init(&sm.in_empty[i], 1);
         }
         mbar_init(&sm.ds_full, kComputeThreads);
-        mbar_init(&sm.stats_full[0], 32);
-        mbar_init(&sm.stats_full[1], 32);
-        mbar_init(&sm.stats_free[0], kComputeThreads / 32);
-        mbar_init(&sm.stats_free[1], kComputeThreads / 32);
-        mbar_init(&sm.kv_tmem, kComputeThreads);
-        mbar_init(&sm.out_full, kComputeThreads);
-        mbar_init(&sm.out_free, 1);
-        mbar_init(&sm.kv_out_full, kComputeThreads);
         fence_barrier_init();
-        // This thread is also the TMA producer: K, V and the first Q/dO half tiles are requested
-        // right away, while the other warps are still setting up (but not before the kernel that
-        // wrote them has completed).
-        pdl_wait();
-        fence_proxy_async_smem();
-        tma_prefetch_desc(&map_x);
-        tma_prefetch_desc(&map_do);
-        const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
-        mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
-        for (int hf = 0; hf < 2; hf++) {
-            for (int pl = 0; pl < 2; pl++) {
-                tma_load_4d(sm.k[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xk, jt * kTile + hf * kHalf, b, pl);
-                tma_load_4d(sm.v[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, xv, jt * kTile + hf * kHalf, b, pl);
-            }
-        }
-        for (int t = 0; t < kSlots && t < 2 * niter; t++) {
-            const int y = (jt + (t >> 1)) * kTile + (t & 1) * kHalf;
-            mbar_expect_tx(&sm.in_full[t], 4 * kPlaneHalf);
-            tma_load_4d(sm.in[t][0], &map_x, &sm.in_full[t], xq, y, b, 0);
-            tma_load_4d(sm.in[t][1], &map_x, &sm.in_full[t], xq, y, b, 1);
-            tma_load_4d(sm.in[t][2], &map_do, &sm.in_full[t], h * kD, y, b, 0);
-            tma_load_4d(sm.in[t][3], &map_do, &sm.in_full[t], h * kD, y, b, 1);
-        }
     }
     if (warp == 2) {
         tmem_alloc(&sm.tmem_base, kTmemCols);
@@ -249,23 +248,78 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = sm.tmem_base;
+    // The CTA owns all 512 columns of its SM's tensor memory, so the allocation starts at column 0, lane 0.
+    // Using that as a constant keeps every tensor-memory address of the MMA issue loops out of the per-lane
+    // registers (an address loaded from shared memory has to be moved to a uniform register before every
+    // instruction that takes it); an allocation anywhere else is reported and the CTA does nothing.
+    constexpr uint32_t tmem = 0;
+    const bool tmem_ok = sm.tmem_base == tmem;
+    WorkList work(BH, nt);
+    Work w;
 
-    if (warp == 0) {
+    if (!tmem_ok) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_TMEM_BASE);
+    } else if (warp == 0) {
         // ------------------------------ TMA producer (boxes of 64 rows) ------------------------------
         if (lane == 0) {
-            const int xq = h * kD;
-            // Half tile t = 2n + half goes to slot t % 3 (the first three were requested during
-            // set-up); a slot is free again once the dV / dK products that read it have completed.
-            for (int t = kSlots, slot = 0, use = 1; t < 2 * niter; t++) {
-                if (!mbar_wait(&sm.in_empty[slot], (use - 1) & 1, ctx, SITE_IN_EMPTY)) break;
-                const int y = (jt + (t >> 1)) * kTile + (t & 1) * kHalf;
+            tma_prefetch_desc(&map_x);
+            tma_prefetch_desc(&map_do);
+            // Half tile number g of the whole launch goes to ring slot g % 3; the slot is free again once
+            // the dV / dK products that read its previous content have completed.
+            uint32_t g = 0;
+            bool ok = true;
+            auto load_half = [&](const Work &it, int t) {
+                const uint32_t slot = g % kSlots;
+                if (g >= (uint32_t)kSlots && !mbar_wait(&sm.in_empty[slot], (g / kSlots - 1) & 1, ctx, SITE_IN_EMPTY)) {
+                    ok = false;
+                    return;
+                }
+                const int b = it.bh / H, h = it.bh % H;
+                const int y = (it.jt + (t >> 1)) * kTile + (t & 1) * kHalf;
                 mbar_expect_tx(&sm.in_full[slot], 4 * kPlaneHalf);
-                tma_load_4d(sm.in[slot][0], &map_x, &sm.in_full[slot], xq, y, b, 0);
-                tma_load_4d(sm.in[slot][1], &map_x, &sm.in_full[slot], xq, y, b, 1);
+                tma_load_4d(sm.in[slot][0], &map_x, &sm.in_full[slot], h * kD, y, b, 0);
+                tma_load_4d(sm.in[slot][1], &map_x, &sm.in_full[slot], h * kD, y, b, 1);
                 tma_load_4d(sm.in[slot][2], &map_do, &sm.in_full[slot], h * kD, y, b, 0);
                 tma_load_4d(sm.in[slot][3], &map_do, &sm.in_full[slot], h * kD, y, b, 1);
-                if (++slot == kSlots) { slot = 0; use++; }
+                g++;
+            };
+            auto load_kv = [&](const Work &it, uint8_t (*dst)[kPlaneTile], int x0) {
+                const int b = it.bh / H;
+                for (int hf = 0; hf < 2; hf++)
+                    for (int pl = 0; pl < 2; pl++)
+                        tma_load_4d(dst[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, x0, it.jt * kTile + hf * kHalf, b, pl);
+            };
+            Work nxt;
+            bool has = work.next(w);
+            if (has) {
+                mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
+                load_kv(w, sm.k, C + (w.bh % H) * kD);
+                load_kv(w, sm.v, 2 * C + (w.bh % H) * kD);
+            }
+            int pre = 0;  // half tiles of the current item already requested
+            for (uint32_t item = 0; has && ok; item++) {
+                for (int t = pre; ok && t < 2 * w.niter; t++) load_half(w, t);
+                const bool has_next = work.next(nxt);
+                pre = 0;
+                if (has_next && ok) {
+                    // The next item's tiles, each as soon as its destination is free: the first Q/dO half
+                    // tile behind the third last one of this item, V behind the last dP^T product, K behind
+                    // the last dQ product.
+                    const int xh = (nxt.bh % H) * kD;
+                    load_half(nxt, 0);
+                    if (ok && !mbar_wait(&sm.v_free, item & 1, ctx, SITE_V_FREE)) ok = false;
+                    if (ok) {
+                        mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
+                        load_kv(nxt, sm.v, 2 * C + xh);
+                    }
+                    if (ok && !mbar_wait(&sm.k_free, item & 1, ctx, SITE_K_FREE)) ok = false;
+                    if (ok) load_kv(nxt, sm.k, C + xh);
+                    // the other two ring slots stage this item's dK / dV tiles on their way out
+                    if (ok && !mbar_wait(&sm.stage_free, item & 1, ctx, SITE_STAGE_FREE)) ok = false;
+                    pre = 1;
+                }
+                w = nxt;
+                has = has_next;
             }
         }
     } else if (warp == 1) {
@@ -276,137 +330,144 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint64_t v_km[2] = {smem_desc_sw128(smem_u32(sm.v[0]), 16, 1024), smem_desc_sw128(smem_u32(sm.v[1]), 16, 1024)};
         // Q/dO ring: descriptors of slot 0, plane 0; slot s, plane p lies (4 s + p) * 8 KiB further
         const uint64_t in_km = smem_desc_sw128(smem_u32(sm.in[0][0]), 16, 1024);
-
-        // Score tasks t = 2n + half, in order: S^T and dP^T of one half of a query tile.  Task t
-        // overwrites the columns task t-2 produced, so the dV / dK products that consumed those
-        // (gradient task t-2, issued by another warp) must have completed.
-        bool ok = mbar_wait_warp(&sm.kv_tmem, 0, ctx, SITE_KV_TMEM);
-        tc_fence_after_sync();
         const uint32_t leader = elect_leader();  // the one lane that issues every MMA and commit of this warp
-        int s_slot = 0, s_use = 0, e_slot = 0, e_use = 0;
-        for (int t = 0; ok && t < 2 * niter; t++) {
-            const int hf = t & 1;
-            [[maybe_unused]] const int n = t >> 1;  // only the trace build reads it
-            if (t >= 2) {
-                ok = mbar_wait_warp(&sm.in_empty[e_slot], e_use & 1, ctx, SITE_IN_EMPTY);
-                if (++e_slot == kSlots) { e_slot = 0; e_use++; }
-            }
-            ok = ok && mbar_wait_warp(&sm.in_full[s_slot], s_use & 1, ctx, SITE_IN_FULL);
-            if (!ok) break;
-            const uint64_t q_km = desc_advance(in_km, s_slot * 4 * kPlaneHalf);
-            const uint64_t g_km = desc_advance(q_km, 2 * kPlaneHalf);
-            tc_fence_after_sync();
-            BWD_TRACE(lane == 0, 0, n, 0 + 4 * hf);
-            uint32_t acc = 0;
+
+        // Score tasks in order: S^T and dP^T of one half of a query tile.  Task g (numbered over the
+        // whole launch) overwrites the columns task g-2 produced, so the dV / dK products that consumed
+        // those (gradient task g-2, issued by another warp) must have completed.
+        uint32_t g = 0;
+        bool ok = true;
+        for (uint32_t item = 0; ok && work.next(w); item++) {
+            ok = mbar_wait_warp(&sm.kv_tmem, item & 1, ctx, SITE_KV_TMEM);
+            for (int t = 0; ok && t < 2 * w.niter; t++, g++) {
+                const int hf = t & 1;
+                const uint32_t slot = g % kSlots;
+                if (g >= 2) ok = mbar_wait_warp(&sm.in_empty[(g - 2) % kSlots], ((g - 2) / kSlots) & 1, ctx, SITE_IN_EMPTY);
+                ok = ok && mbar_wait_warp(&sm.in_full[slot], (g / kSlots) & 1, ctx, SITE_IN_FULL);
+                if (!ok) break;
+                const uint64_t q_km = desc_advance(in_km, slot * 4 * kPlaneHalf);
+                const uint64_t g_km = desc_advance(q_km, 2 * kPlaneHalf);
+                tc_fence_after_sync();
+                uint32_t acc = 0;
 #pragma unroll
-            for (int term = 0; term < 3; term++) {
-                const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; kk++) {
-                    if (term < 2)
-                        mma_ts_lead(leader, tmem + kColST + hf * kHalf, tmem + kColKH + 8 * kk,
-                                     desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
-                    else
-                        mma_ss_lead(leader, tmem + kColST + hf * kHalf, desc_advance(k_km[a], kk * 32),
-                                     desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
-                    acc = 1;
+                    for (int kk = 0; kk < kD / 16; kk++) {
+                        if (term < 2)
+                            mma_ts_lead(leader, tmem + kColST + hf * kHalf, tmem + kColKH + 8 * kk,
+                                         desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                        else
+                            mma_ss_lead(leader, tmem + kColST + hf * kHalf, desc_advance(k_km[a], kk * 32),
+                                         desc_advance(q_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                        acc = 1;
+                    }
                 }
-            }
-            acc = 0;
+                acc = 0;
 #pragma unroll
-            for (int term = 0; term < 3; term++) {
-                const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; kk++) {
-                    if (term < 2)
-                        mma_ts_lead(leader, tmem + kColDPT + hf * kHalf, tmem + kColVH + 8 * kk,
-                                     desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
-                    else
-                        mma_ss_lead(leader, tmem + kColDPT + hf * kHalf, desc_advance(v_km[a], kk * 32),
-                                     desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
-                    acc = 1;
+                    for (int kk = 0; kk < kD / 16; kk++) {
+                        if (term < 2)
+                            mma_ts_lead(leader, tmem + kColDPT + hf * kHalf, tmem + kColVH + 8 * kk,
+                                         desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                        else
+                            mma_ss_lead(leader, tmem + kColDPT + hf * kHalf, desc_advance(v_km[a], kk * 32),
+                                         desc_advance(g_km, bb * kPlaneHalf + kk * 32), idesc_st, acc);
+                        acc = 1;
+                    }
                 }
+                tc_commit_lead(leader, &sm.st_full[hf]);
+                if (t == 2 * w.niter - 1) tc_commit_lead(leader, &sm.v_free);
             }
-            tc_commit_lead(leader, &sm.st_full[hf]);
-            BWD_TRACE(lane == 0, 0, n, 1 + 4 * hf);
-            if (++s_slot == kSlots) { s_slot = 0; s_use++; }
         }
     } else if (warp == 2) {
         // ------------------------------ row statistics and output copies ------------------------------
-        // Two small jobs polled by one warp.  (1) -lse * log2(e) and -delta of every query tile,
-        // double buffered in shared memory; each buffer has its own full / free barriers, so this
-        // warp can never be two phases ahead of a reader of the same barrier.  (2) Staged dQ tiles
-        // are added into dqkv (several key tiles contribute to one query tile), the final dK / dV
-        // tiles are plain stores; rows past the end of the sequence are dropped by the copy engine.
+        // Two small jobs, taken in the fixed order in which the compute warps make them ready.
+        // (1) -lse * log2(e) and -delta of every query tile, double buffered in shared memory: tile n
+        // (numbered over the whole launch) goes to buffer n % 2 once every compute warp has released tile
+        // n - 2; each buffer has its own full / free barriers, so this warp is never two phases ahead of a
+        // reader.  (2) Staged dQ tiles are added into dqkv (several key tiles contribute to one query
+        // tile), the dK / dV tiles of a finished item are plain stores; rows past the end of the sequence
+        // are dropped by the copy engine.
         if (lane == 0) tma_prefetch_desc(&map_dx);
-        const int xq = h * kD, xk = C + h * kD, xv = 2 * C + h * kD;
-        int m = 0, o = 0;
-        bool kv_stored = false, ok = true;
-        uint64_t idle_since = 0;
-        uint32_t idle_polls = 0;
-        while (ok && !(kv_stored && o == niter)) {
-            bool progressed = false;
-            if (m < niter) {
-                const int buf = m & 1;
-                if (m < 2 || __all_sync(0xffffffffu, mbar_test_wait(&sm.stats_free[buf], ((m >> 1) - 1) & 1))) {
+        struct TileCursor {  // the query tiles of this CTA's items, in processing order
+            WorkList wl;
+            Work w;
+            int m;
+            bool valid;
+            __device__ TileCursor(int BH_, int nt_) : wl(BH_, nt_), m(0) { valid = wl.next(w); }
+            __device__ void advance() {
+                if (++m >= w.niter) {
+                    m = 0;
+                    valid = wl.next(w);
+                }
+            }
+        };
+        TileCursor cur(BH, nt), ahead(BH, nt);
+        auto stage_stats = [&](const TileCursor &c, uint32_t n) {
+            const int buf = n & 1;
 #pragma unroll
-                    for (int k = 0; k < kTile / 32; k++) {
-                        const int r = lane + 32 * k, t = (jt + m) * kTile + r;
-                        sm.lse2[buf][r] = t < T ? -lse[(size_t)bh * T + t] * 1.4426950408889634f : 0.f;
-                        sm.delta[buf][r] = t < T ? -delta[(size_t)bh * T + t] : 0.f;
-                    }
-                    mbar_arrive(&sm.stats_full[buf]);
-                    m++;
-                    progressed = true;
-                }
+            for (int k = 0; k < kTile / 32; k++) {
+                const int r = lane + 32 * k, t = (c.w.jt + c.m) * kTile + r;
+                sm.lse2[buf][r] = t < T ? -lse[(size_t)c.w.bh * T + t] * 1.4426950408889634f : 0.f;
+                sm.delta[buf][r] = t < T ? -delta[(size_t)c.w.bh * T + t] : 0.f;
             }
-            if (o < niter) {
-                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.out_full, o & 1))) {
-                    if (lane == 0) {
-                        tma_reduce_add_3d(sm.ds[0][0], &map_dx, xq, (jt + o) * kTile, b);
-                        tma_reduce_add_3d(sm.ds[0][1], &map_dx, xq + 32, (jt + o) * kTile, b);
-                        bulk_commit();
-                        if (o == niter - 1) BWD_EPI2(1);
-                        bulk_wait_read_all();
-                        if (o == niter - 1) BWD_EPI2(5);
-                        mbar_arrive(&sm.out_free);
-                    }
-                    __syncwarp();
-                    o++;
-                    progressed = true;
-                }
-            }
-            if (!kv_stored && __all_sync(0xffffffffu, mbar_test_wait(&sm.kv_out_full, 0))) {
-                if (lane == 0) {
-                    tma_store_3d(sm.in[0][0], &map_dx, xk, jt * kTile, b);
-                    tma_store_3d(sm.in[0][2], &map_dx, xk + 32, jt * kTile, b);
-                    tma_store_3d(sm.in[1][0], &map_dx, xv, jt * kTile, b);
-                    tma_store_3d(sm.in[1][2], &map_dx, xv + 32, jt * kTile, b);
-                    bulk_commit();
-                    BWD_EPI2(6);
-                }
-                kv_stored = true;
-                progressed = true;
-            }
-            if (progressed) {
-                idle_polls = 0;
-            } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up when nothing became ready for a second
-                const uint64_t now = global_timer_ns();
-                if (idle_polls == 256u) idle_since = now;
-                const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
-                if (__any_sync(0xffffffffu, give_up)) {
-                    if (lane == 0 && !sm.abort_flag) {
-                        sm.abort_flag = 1;
-                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_OUT_FULL);
-                    }
-                    ok = false;
-                }
-            }
+            mbar_arrive(&sm.stats_full[buf]);
+        };
+        for (uint32_t n = 0; n < 2 && ahead.valid; n++) {
+            stage_stats(ahead, n);
+            ahead.advance();
         }
-        // Shared memory must stay alive until the copies have read it; the writes themselves
-        // complete on their own before the grid does.
+        // the staged dQ tile of query tile `qt` -> dq third of dqkv
+        auto reduce_dq = [&](const Work &it, int qt) {
+            if (lane == 0) {
+                const int b = it.bh / H, xq = (it.bh % H) * kD;
+                tma_reduce_add_3d(sm.ds[0][0], &map_dx, xq, qt * kTile, b);
+                tma_reduce_add_3d(sm.ds[0][1], &map_dx, xq + 32, qt * kTile, b);
+                bulk_commit();
+                bulk_wait_read_all();
+                mbar_arrive(&sm.out_free);
+            }
+            __syncwarp();
+        };
+        bool ok = true;
+        uint32_t item = 0;  // items finished
+        for (uint32_t n = 0; ok && cur.valid; n++) {
+            if (cur.m >= 1) {  // dQ of the item's previous query tile (staged after half A of this one)
+                if (!mbar_wait_warp(&sm.out_full, (n - 1) & 1, ctx, SITE_OUT_FULL)) break;
+                reduce_dq(cur.w, cur.w.jt + cur.m - 1);
+            }
+            if (ahead.valid) {  // statistics two tiles ahead, into the buffer tile n releases
+                if (!mbar_wait_warp(&sm.stats_free[n & 1], (n >> 1) & 1, ctx, SITE_STATS_FREE)) break;
+                stage_stats(ahead, n + 2);
+                ahead.advance();
+            }
+            if (cur.m == cur.w.niter - 1) {  // end of the item: dK and dV, then the last dQ
+                if (!mbar_wait_warp(&sm.kv_out_full, item & 1, ctx, SITE_KV_OUT_FULL)) break;
+                if (lane == 0) {
+                    // the ring slots of the item's last two half tiles (numbers 2n and 2n + 1 of the launch)
+                    const uint32_t s_k = (2 * n) % kSlots, s_v = (2 * n + 1) % kSlots;
+                    const int b = cur.w.bh / H, xk = C + (cur.w.bh % H) * kD, xv = xk + C;
+                    tma_store_3d(sm.in[s_k][0], &map_dx, xk, cur.w.jt * kTile, b);
+                    tma_store_3d(sm.in[s_k][2], &map_dx, xk + 32, cur.w.jt * kTile, b);
+                    tma_store_3d(sm.in[s_v][0], &map_dx, xv, cur.w.jt * kTile, b);
+                    tma_store_3d(sm.in[s_v][2], &map_dx, xv + 32, cur.w.jt * kTile, b);
+                    bulk_commit();
+                    bulk_wait_read_all();
+                    mbar_arrive(&sm.stage_free);
+                }
+                __syncwarp();
+                if (!mbar_wait_warp(&sm.out_full, n & 1, ctx, SITE_OUT_FULL)) break;
+                reduce_dq(cur.w, cur.w.jt + cur.m);
+                item++;
+            }
+            cur.advance();
+        }
+        // Shared memory must stay alive until the copies have read it (they have: every group was waited
+        // for above); the writes themselves complete on their own before the grid does.
         if (lane == 0) bulk_wait_read_all();
-        if (lane == 0) BWD_EPI2(7);
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------ compute group ------------------------------
@@ -416,7 +477,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint32_t lane_addr = (uint32_t)(quarter << 5) << 16;
         const uint32_t t_st = tmem + lane_addr + kColST + 16 * cq;
         const uint32_t t_dpt = tmem + lane_addr + kColDPT + 16 * cq;
+        const float2 sc2 = make_float2(scale_log2, scale_log2);
         bool ok = true;
+        uint32_t n = 0;  // query tiles processed so far in this launch
 
         // One row (16 of its 64 columns) of an fp32 output tile into the staging layout the copy
         // engine expects: two 32-column halves, 128-byte rows, 16-byte chunks swizzled by row % 8.
@@ -430,9 +493,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                                 __uint_as_float(r[4 * e + 2]) * f, __uint_as_float(r[4 * e + 3]) * f);
             }
         };
-        // dQ of iteration n (its barrier phase has been waited for): scale this thread's 16 columns
-        // into the staging tile; warp 3 adds the tile into dqkv with one bulk reduction per half.
-        auto flush_dq = [&](int n) -> bool {
+        // dQ of the last query tile (its barrier phase has been waited for): scale this thread's 16 columns
+        // into the staging tile; warp 2 adds the tile into dqkv with one bulk reduction per half.
+        auto flush_dq = [&]() {
             tc_fence_after_sync();
             uint32_t r[16];
             tmem_ld16(tmem + lane_addr + kColDQ + 16 * cq, r);
@@ -440,107 +503,97 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             stage_row(sm.ds[0][0], r, scale);
             fence_proxy_async_smem();
             mbar_arrive(&sm.out_full);
-            return true;
         };
 
-        // K hi and V hi, this thread's 16 head-dim values of key `row`, into tensor memory (packed
-        // pairs, so 8 columns each); the rows in shared memory are 128-byte swizzled.
-        if (!mbar_wait_warp(&sm.kv_full, 0, ctx, SITE_KV_FULL)) ok = false;
-        if (ok) {
-            uint32_t kh[8], vh[8];
+        for (uint32_t item = 0; ok && work.next(w); item++) {
+            // K hi and V hi, this thread's 16 head-dim values of key `row`, into tensor memory (packed
+            // pairs, so 8 columns each); the rows in shared memory are 128-byte swizzled.  The previous
+            // item's last score products, the readers of these columns, completed before this thread left
+            // that item's loop.
+            if (!mbar_wait_warp(&sm.kv_full, item & 1, ctx, SITE_KV_FULL)) { ok = false; break; }
+            {
+                uint32_t kh[8], vh[8];
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int off = row * 128 + (((2 * cq + j) ^ (row & 7)) << 4);
-                const uint4 a = *reinterpret_cast<const uint4 *>(sm.k[0] + off);
-                const uint4 c = *reinterpret_cast<const uint4 *>(sm.v[0] + off);
-                kh[4 * j] = a.x, kh[4 * j + 1] = a.y, kh[4 * j + 2] = a.z, kh[4 * j + 3] = a.w;
-                vh[4 * j] = c.x, vh[4 * j + 1] = c.y, vh[4 * j + 2] = c.z, vh[4 * j + 3] = c.w;
-            }
-            tmem_st8(tmem + lane_addr + kColKH + 8 * cq, kh);
-            tmem_st8(tmem + lane_addr + kColVH + 8 * cq, vh);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.kv_tmem);
-        }
-        BWD_LIFE(1);
-        const float2 sc2 = make_float2(scale_log2, scale_log2);
-        for (int n = 0; ok && n < niter; n++) {
-            const bool diag = (n == 0);
-            const int lb = n & 1;
-            // row statistics of this query tile (warp 2 stages them up to two tiles ahead)
-            if (!mbar_wait_warp(&sm.stats_full[lb], (n >> 1) & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
-
-            uint32_t dh_a[8], dl_a[8], dh_b[8], dl_b[8];
-            // half A: queries 0..63 of the tile
-            BWD_TRACE(threadIdx.x == 128, 1, n, 0);
-            if (!mbar_wait_warp(&sm.st_full[0], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
-            tc_fence_after_sync();
-            BWD_TRACE(threadIdx.x == 128, 1, n, 1);
-            compute_run(sm, t_st, t_dpt, lb, 16 * cq, row, diag, sc2, dh_a, dl_a);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.pds_full[0]);  // dV / dK of half A may start; dS^T goes to shared memory below
-            BWD_TRACE(threadIdx.x == 128, 1, n, 2);
-            // While the tensor cores work on half B's scores: the previous tile's dQ (issued as soon as
-            // its dS^T was stored) has finished by now; move it out.  The copy engine reads the staged
-            // tile while half B is computed, then dS^T of this tile may overwrite it.
-            if (n >= 1) {
-                if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
-                    ok = false;
-                    break;
+                for (int j = 0; j < 2; j++) {
+                    const int off = row * 128 + (((2 * cq + j) ^ (row & 7)) << 4);
+                    const uint4 a = *reinterpret_cast<const uint4 *>(sm.k[0] + off);
+                    const uint4 c = *reinterpret_cast<const uint4 *>(sm.v[0] + off);
+                    kh[4 * j] = a.x, kh[4 * j + 1] = a.y, kh[4 * j + 2] = a.z, kh[4 * j + 3] = a.w;
+                    vh[4 * j] = c.x, vh[4 * j + 1] = c.y, vh[4 * j + 2] = c.z, vh[4 * j + 3] = c.w;
                 }
-                if (!flush_dq(n - 1)) { ok = false; break; }
+                tmem_st8(tmem + lane_addr + kColKH + 8 * cq, kh);
+                tmem_st8(tmem + lane_addr + kColVH + 8 * cq, vh);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.kv_tmem);
             }
-            BWD_TRACE(threadIdx.x == 128, 1, n, 7);
-            // half B: queries 64..127
-            if (!mbar_wait_warp(&sm.st_full[1], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
-            tc_fence_after_sync();
-            BWD_TRACE(threadIdx.x == 128, 1, n, 3);
-            compute_run(sm, t_st + kHalf, t_dpt + kHalf, lb, kHalf + 16 * cq, row, diag, sc2, dh_b, dl_b);
-            BWD_TRACE(threadIdx.x == 128, 1, n, 4);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.pds_full[1]);  // dV / dK of half B may start
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.stats_free[lb]);  // this warp has read the tile's statistics
-            BWD_TRACE(threadIdx.x == 128, 1, n, 5);
-            // the staged dQ tile of the previous iteration must have left shared memory
-            if (n >= 1 && !mbar_wait_warp(&sm.out_free, (n - 1) & 1, ctx, SITE_OUT_FREE)) { ok = false; break; }
-            store_ds(sm.ds[0][0], sm.ds[1][0], row, cq, dh_a, dl_a);
-            store_ds(sm.ds[0][1], sm.ds[1][1], row, cq, dh_b, dl_b);
-            fence_proxy_async_smem();
-            mbar_arrive(&sm.ds_full);  // dQ may start
-            BWD_TRACE(threadIdx.x == 128, 1, n, 6);
-        }
+            for (int m = 0; ok && m < w.niter; m++, n++) {
+                const bool diag = (m == 0);
+                const int lb = n & 1;
+                // row statistics of this query tile (warp 2 stages them up to two tiles ahead)
+                if (!mbar_wait_warp(&sm.stats_full[lb], (n >> 1) & 1, ctx, SITE_ROW_BAR)) { ok = false; break; }
 
-        BWD_LIFE(2);
-        BWD_EPI(0);
-        // Epilogue.  Once the last dV / dK products have completed the Q/dO ring is dead: its space
-        // stages the dK and dV tiles for the copy engine while the last dQ product still runs.
-        const int last = 2 * niter - 1;
-        if (ok && mbar_wait_warp(&sm.in_empty[last % kSlots], (last / kSlots) & 1, ctx, SITE_IN_EMPTY)) {
-            tc_fence_after_sync();
-            uint32_t rk[16], rv[16];
-            tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
-            tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
-            tmem_wait_ld();
-            BWD_EPI(3);
-            stage_row(sm.in[0][0], rk, scale);
-            stage_row(sm.in[1][0], rv, 1.f);
-            fence_proxy_async_smem();
-            mbar_arrive(&sm.kv_out_full);
-            BWD_EPI(4);
-            if (mbar_wait_warp(&sm.dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) {
-                flush_dq(niter - 1);
-                BWD_EPI(2);
+                uint32_t dh_a[8], dl_a[8], dh_b[8], dl_b[8];
+                // half A: queries 0..63 of the tile
+                if (!mbar_wait_warp(&sm.st_full[0], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+                tc_fence_after_sync();
+                compute_run(sm, t_st, t_dpt, lb, 16 * cq, row, diag, sc2, dh_a, dl_a);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.pds_full[0]);  // dV / dK of half A may start; dS^T goes to shared memory below
+                // While the tensor cores work on half B's scores: the previous tile's dQ (issued as soon as
+                // its dS^T was stored) has finished by now; move it out.  The copy engine reads the staged
+                // tile while half B is computed, then dS^T of this tile may overwrite it.
+                if (m >= 1) {
+                    if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_FREE)) {
+                        ok = false;
+                        break;
+                    }
+                    flush_dq();
+                }
+                // half B: queries 64..127
+                if (!mbar_wait_warp(&sm.st_full[1], n & 1, ctx, SITE_ST_FULL)) { ok = false; break; }
+                tc_fence_after_sync();
+                compute_run(sm, t_st + kHalf, t_dpt + kHalf, lb, kHalf + 16 * cq, row, diag, sc2, dh_b, dl_b);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.pds_full[1]);  // dV / dK of half B may start
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.stats_free[lb]);  // this warp has read the tile's statistics
+                // the staged dQ tile of the previous query tile (of this item or the one before) must have left
+                // shared memory
+                if (n >= 1 && !mbar_wait_warp(&sm.out_free, (n - 1) & 1, ctx, SITE_OUT_FREE)) { ok = false; break; }
+                store_ds(sm.ds[0][0], sm.ds[1][0], row, cq, dh_a, dl_a);
+                store_ds(sm.ds[0][1], sm.ds[1][1], row, cq, dh_b, dl_b);
+                fence_proxy_async_smem();
+                mbar_arrive(&sm.ds_full);  // dQ may start
             }
+            if (!ok) break;
+
+            // End of the item.  Once the last dV / dK products have completed the Q/dO ring is dead except
+            // for the slot the producer refills first: the slots of the item's last two half tiles stage
+            // the dK and dV tiles for the copy engine while the last dQ product still runs; then that dQ.
+            if (!mbar_wait_warp(&sm.grads_done, item & 1, ctx, SITE_GRADS_DONE)) { ok = false; break; }
+            tc_fence_after_sync();
+            {
+                uint32_t rk[16], rv[16];
+                tmem_ld16(tmem + lane_addr + kColDK + 16 * cq, rk);
+                tmem_ld16(tmem + lane_addr + kColDV + 16 * cq, rv);
+                tmem_wait_ld();
+                stage_row(sm.in[(2 * n - 2) % kSlots][0], rk, scale);
+                stage_row(sm.in[(2 * n - 1) % kSlots][0], rv, 1.f);
+                fence_proxy_async_smem();
+                mbar_arrive(&sm.kv_out_full);
+            }
+            if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) { ok = false; break; }
+            flush_dq();
+            tc_fence_before_sync();  // the reads above are ordered before the next item's arrivals
         }
     } else if (warp == kGradWarp) {
         // ------------------------------ MMA issuer: dV, dK, dQ ------------------------------
-        // Two task streams, each in order: gradient tasks g = 2n + half (dV, dK of one half, once the
-        // compute warps have turned that half into P^T / dS^T) and one dQ task per query tile (once
-        // dS^T is in shared memory).  Whichever is ready goes first, dQ before dV / dK: the compute
-        // warps need its result, and its operand buffer, one tile later.
+        // Per query tile, in the order the operands become ready: dV, dK of half A, of half B (once the
+        // compute warps have turned that half into P^T / dS^T), then dQ of the tile (once dS^T is in shared
+        // memory).
         constexpr uint32_t idesc_kv = idesc_bf16_f32(kTile, kD, 0, 1);  // dV, dK (A in TMEM)
         constexpr uint32_t idesc_dq = idesc_bf16_f32(kTile, kD, 1, 1);  // dQ (A, B MN-major)
         // MN-major views: the row index is the contraction index
@@ -548,43 +601,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint64_t k_mn[2] = {smem_desc_sw128(smem_u32(sm.k[0]), 1024, 1024), smem_desc_sw128(smem_u32(sm.k[1]), 1024, 1024)};
         const uint64_t ds_mn[2] = {smem_desc_sw128(smem_u32(sm.ds[0][0]), kPlaneTile, 1024),
                                    smem_desc_sw128(smem_u32(sm.ds[1][0]), kPlaneTile, 1024)};
-        const int ntask = 2 * niter;
-        int g_idx = 0, d_idx = 0, g_slot = 0;
         const uint32_t leader = elect_leader();
+        uint32_t g = 0, n = 0;  // half tiles / query tiles issued so far in this launch
         bool ok = true;
-        uint64_t idle_since = 0;
-        uint32_t idle_polls = 0;
-        while (ok && d_idx < niter) {
-            bool progressed = false;
-            if (2 * d_idx + 1 < g_idx) {
-                // dQ_i = dS K_j over all 128 keys
-                const int n = d_idx;
-                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.ds_full, n & 1))) {
+        while (ok && work.next(w)) {
+            for (int m = 0; ok && m < w.niter; m++, n++) {
+                for (int hf = 0; hf < 2; hf++, g++) {
+                    if (!mbar_wait_warp(&sm.pds_full[hf], n & 1, ctx, SITE_PDS_FULL)) { ok = false; break; }
                     tc_fence_after_sync();
-                    BWD_TRACE(lane == 0, 1, 8 + (n & 7), 0);
-                    const uint32_t d_q = tmem + kColDQ;
-#pragma unroll
-                    for (int term = 0; term < 3; term++) {
-                        const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
-#pragma unroll
-                        for (int kk = 0; kk < kTile / 16; kk++) {
-                            mma_ss_lead(leader, d_q, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048),
-                                        idesc_dq, (term > 0 || kk > 0) ? 1u : 0u);
-                        }
-                    }
-                    tc_commit_lead(leader, &sm.dq_full[n & 1]);
-                    BWD_TRACE(lane == 0, 1, 8 + (n & 7), 1);
-                    d_idx++;
-                    progressed = true;
-                }
-            }
-            if (g_idx < ntask) {
-                const int n = g_idx >> 1, hf = g_idx & 1;
-                if (__all_sync(0xffffffffu, mbar_test_wait(&sm.pds_full[hf], n & 1))) {
-                    tc_fence_after_sync();
-                    const uint64_t q_mn = desc_advance(in_mn, g_slot * 4 * kPlaneHalf);
+                    const uint32_t slot = g % kSlots;
+                    const uint64_t q_mn = desc_advance(in_mn, slot * 4 * kPlaneHalf);
                     const uint64_t g_mn = desc_advance(q_mn, 2 * kPlaneHalf);
-                    BWD_TRACE(lane == 0, 0, n, 2 + 4 * hf);
+                    const bool first = (m == 0 && hf == 0);  // the item's accumulators start from zero
                     // dV += P^T dO_i over this half's 64 queries (4 K-steps of 16)
 #pragma unroll
                     for (int term = 0; term < 3; term++) {
@@ -592,8 +620,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #pragma unroll
                         for (int k4 = 0; k4 < 4; k4++) {
                             const int kk = 4 * hf + k4;
-                            mma_ts_lead(leader, tmem + kColDV, tmem + kColST + 16 * kk + 8 * a, desc_advance(g_mn, bb * kPlaneHalf + k4 * 2048),
-                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                            mma_ts_lead(leader, tmem + kColDV, tmem + kColST + 16 * kk + 8 * a,
+                                        desc_advance(g_mn, bb * kPlaneHalf + k4 * 2048), idesc_kv,
+                                        (!first || term > 0 || k4 > 0) ? 1u : 0u);
                         }
                     }
                     // dK += dS^T Q_i
@@ -603,59 +632,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #pragma unroll
                         for (int k4 = 0; k4 < 4; k4++) {
                             const int kk = 4 * hf + k4;
-                            mma_ts_lead(leader, tmem + kColDK, tmem + kColDPT + 16 * kk + 8 * a, desc_advance(q_mn, bb * kPlaneHalf + k4 * 2048),
-                                         idesc_kv, (g_idx > 0 || term > 0 || k4 > 0) ? 1u : 0u);
+                            mma_ts_lead(leader, tmem + kColDK, tmem + kColDPT + 16 * kk + 8 * a,
+                                        desc_advance(q_mn, bb * kPlaneHalf + k4 * 2048), idesc_kv,
+                                        (!first || term > 0 || k4 > 0) ? 1u : 0u);
                         }
                     }
-                    tc_commit_lead(leader, &sm.in_empty[g_slot]);
-                    if (++g_slot == kSlots) g_slot = 0;
-                    BWD_TRACE(lane == 0, 0, n, 3 + 4 * hf);
-                    g_idx++;
-                    progressed = true;
+                    tc_commit_lead(leader, &sm.in_empty[slot]);
+                    if (m == w.niter - 1 && hf == 1) tc_commit_lead(leader, &sm.grads_done);
                 }
-            }
-            if (progressed) {
-                idle_polls = 0;
-            } else if ((++idle_polls & 255u) == 0u) {  // bounded: give up when nothing became ready for a second
-                const uint64_t now = global_timer_ns();
-                if (idle_polls == 256u) idle_since = now;
-                const bool give_up = (now - idle_since > TC05_WAIT_LIMIT_NS) || sm.abort_flag;
-                if (__any_sync(0xffffffffu, give_up)) {
-                    if (lane == 0 && !sm.abort_flag) {
-                        sm.abort_flag = 1;
-                        if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + SITE_MMA_IDLE);
+                if (!ok) break;
+                // dQ_i = dS K_j over all 128 keys
+                if (!mbar_wait_warp(&sm.ds_full, n & 1, ctx, SITE_DS_FULL)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const int a = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; kk++) {
+                        mma_ss_lead(leader, tmem + kColDQ, desc_advance(ds_mn[a], kk * 2048), desc_advance(k_mn[bb], kk * 2048),
+                                    idesc_dq, (term > 0 || kk > 0) ? 1u : 0u);
                     }
-                    ok = false;
                 }
+                tc_commit_lead(leader, &sm.dq_full[n & 1]);
+                if (m == w.niter - 1) tc_commit_lead(leader, &sm.k_free);
             }
         }
     }
 
     // ------------------------------ tear-down ------------------------------
-    if (sm.abort_flag) __nanosleep(50000);
-    BWD_EPI(4);
+    if (sm.abort_flag) __nanosleep(50000);  // let copies that are still in flight land
     tc_fence_before_sync();
     __syncthreads();
-    BWD_LIFE(3);
     if (warp == 2) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem, kTmemCols);
+        tmem_dealloc(sm.tmem_base, kTmemCols);
     }
 }
 
 }  // namespace
-
-#ifdef ATTN_TRACE
-extern "C" int attn_bwd_trace_read(long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_bwd_trace, sizeof(g_bwd_trace));
-}
-extern "C" int attn_bwd_epi_read(long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_bwd_epi, sizeof(g_bwd_epi));
-}
-extern "C" int attn_bwd_life_read(long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_bwd_life, sizeof(g_bwd_life));
-}
-#endif
 
 static size_t bwd_smem_bytes() { return sizeof(BwdSmem); }
 static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward kernel shared memory");
@@ -665,11 +679,14 @@ cudaError_t fast_bwd_set_attributes() {
 }
 
 // map_x / map_do must have boxes of 64 rows (see the producer warp); map_dx covers dqkv as fp32
-// {3C, T, B} with boxes of 32 columns x 128 rows, 128-byte swizzle.
-cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
-                                 const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s) {
+// {3C, T, B} with boxes of 32 columns x 128 rows, 128-byte swizzle.  `num_sms` CTAs at most: one per SM,
+// each walking its share of the (batch, head, key tile) items.
+cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx,
+                                 const float *lse, const float *delta, float *dqkv, int B, int T, int H, int num_sms,
+                                 int *status, cudaStream_t s) {
     const int nt = (T + kTile - 1) / kTile;
-    const unsigned grid = (unsigned)(nt * B * H);
+    const long long items = (long long)nt * B * H;
+    const unsigned grid = (unsigned)(items < num_sms ? items : num_sms);
     const float scale = 0.125f;  // 1/sqrt(64)
     return launch_after_previous(attn_bwd_kernel, dim3(grid), dim3(kThreads), bwd_smem_bytes(), s, map_x, map_do, map_dx, lse,
                                  delta, dqkv, B, T, H, scale, scale * 1.4426950408889634f, status);

@@ -41,8 +41,9 @@ cudaError_t fast_fwd_set_attributes();
 cudaError_t fast_bwd_set_attributes();
 cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map_out, const CUtensorMap *map_copy,
                                 float *out, float *out_copy, float *lse, int B, int T, int H, int *status, cudaStream_t s);
-cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx, const float *lse,
-                                 const float *delta, float *dqkv, int B, int T, int H, int *status, cudaStream_t s);
+cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx,
+                                 const float *lse, const float *delta, float *dqkv, int B, int T, int H, int num_sms,
+                                 int *status, cudaStream_t s);
 
 // Launches `kernel` so that it may begin (up to its pdl_wait(), tc05.cuh) while the previous kernel of the
 // stream is still running: its launch latency and set-up overlap that kernel's tail.

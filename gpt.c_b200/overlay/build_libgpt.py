@@ -1,17 +1,19 @@
 """Build gpt.c with this repository's attention in place of its own (and, beside it, unmodified).
 
-The reference tree is read where it lies (never copied, its Makefile is not run).  Two builds are
-written under ``oracle/_ref/`` (git-ignored, reference-derived):
+The reference tree is read where it lies (never copied, its Makefile is not run).  The build is
+written under ``gpt.c_b200/overlay/_build/`` (git-ignored):
 
-  oracle/_ref/gptc_overlay/    libgpt.so = reference sources, with src/attention.c,
-                               kernels/src/core/Attention.c and kernels/src/cuda/{Attention,Linear,
-                               LayerNorm,Tensor,GeLU,CrossEntropyLoss,AdamW,Alloc}.cu taken from gpt.c_b200/overlay/, linked
-                               against libattn_sm100.so;
-                               plus train_gpt, infer_gpt and layer_driver
-  oracle/_ref/gptc_reference/  the same executables from the unmodified reference (its cuBLAS + SIMT
-                               attention compiled for sm_100a): the GPU baseline
+  _build/gptc_overlay/   libgpt.so = reference sources, with src/attention.c,
+                         kernels/src/core/Attention.c and kernels/src/cuda/{Attention,Linear,
+                         LayerNorm,Tensor,GeLU,CrossEntropyLoss,AdamW,Alloc}.cu taken from
+                         gpt.c_b200/overlay/, linked against libattn_sm100.so;
+                         plus train_gpt, infer_gpt and layer_driver
 
-    python gpt.c_b200/overlay/build_libgpt.py [--reference DIR] [--only overlay|reference]
+``build(ref, out_dir, overlay=False)`` makes the same executables from the unmodified reference (its
+cuBLAS + SIMT attention compiled for sm_100a); the checker-side recipe ``oracle/build.py`` uses it for
+the GPU baseline it keeps beside the CPU one.
+
+    python gpt.c_b200/overlay/build_libgpt.py --reference DIR      (or GPTC_REFERENCE_DIR=DIR)
 """
 from __future__ import annotations
 
@@ -20,12 +22,40 @@ import glob
 import os
 import subprocess
 import sys
+import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.abspath(os.path.join(HERE, "..", ".."))
-sys.path.insert(0, ROOT)
-from oracle.build import find_openblas  # noqa: E402
+BUILD_DIR = os.path.join(HERE, "_build")
+OVERLAY_OUT = os.path.join(BUILD_DIR, "gptc_overlay")
+
+
+def find_openblas() -> tuple[str, bool] | None:
+    """(path, uses_scipy_prefix) of an LP64 OpenBLAS shared object, or None.  gpt.c takes OpenBLAS from a
+    submodule that is not vendored; the copies inside the Python wheels are what an offline box has."""
+    site = sysconfig.get_paths()["purelib"]
+    hits = sorted(glob.glob(os.path.join(site, "scipy.libs", "libscipy_openblas-*.so")))
+    if hits:
+        return hits[0], True
+    for pat in ("opencv_python_headless.libs/libopenblas*.so*", "numpy.libs/libopenblas*.so*"):
+        hits = sorted(glob.glob(os.path.join(site, pat)))
+        if hits:
+            return hits[0], False
+    for d in ("/usr/lib/x86_64-linux-gnu", "/usr/lib64", "/usr/local/lib"):
+        hits = sorted(glob.glob(os.path.join(d, "libopenblas.so*")))
+        if hits:
+            return hits[0], False
+    return None
+
+
+def reference_dir(explicit: str | None = None) -> str | None:
+    """The gpt.c source tree: --reference, else GPTC_REFERENCE_DIR, else a directory `reference` beside
+    this repository.  None when there is none (the builds are then used as they are)."""
+    for cand in (explicit, os.environ.get("GPTC_REFERENCE_DIR"), os.path.join(ROOT, "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "kernels", "src", "cuda")):
+            return os.path.abspath(cand)
+    return None
 
 ATTN_LIB_DIR = os.path.join(ROOT, "gpt.c_b200", "lib")
 REPLACED = {"src/attention.c", "kernels/src/core/Attention.c", "kernels/src/cuda/Attention.cu",
@@ -46,9 +76,9 @@ def build(ref: str, out_dir: str, overlay: bool) -> str:
     blas_lib, scipy_prefix = blas
     obj_dir = os.path.join(out_dir, "obj")
     os.makedirs(obj_dir, exist_ok=True)
-    inc = ["-I", os.path.join(ROOT, "oracle"), "-I", os.path.join(ref, "include"), "-I", os.path.join(ref, "kernels/include"),
+    inc = ["-I", HERE, "-I", os.path.join(ref, "include"), "-I", os.path.join(ref, "kernels/include"),
            "-I", os.path.join(ref, "kernels/src"), "-I", os.path.join(ROOT, "include")]
-    defs = ["-DOMP"] + (["-DREF_BLAS_SCIPY"] if scipy_prefix else [])
+    defs = ["-DOMP"] + (["-DGPTC_BLAS_SCIPY"] if scipy_prefix else [])
     host_flags = ["-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-w"]
 
     c_srcs, cu_srcs = [], []
@@ -92,19 +122,15 @@ def build(ref: str, out_dir: str, overlay: bool) -> str:
     return out_dir
 
 
-def build_all(ref: str, only: str | None = None) -> dict:
-    out = {}
-    base = os.path.join(ROOT, "oracle", "_ref")
-    if only in (None, "overlay"):
-        out["overlay"] = build(ref, os.path.join(base, "gptc_overlay"), overlay=True)
-    if only in (None, "reference"):
-        out["reference"] = build(ref, os.path.join(base, "gptc_reference"), overlay=False)
-    return out
+def build_overlay(ref: str) -> str:
+    return build(ref, OVERLAY_OUT, overlay=True)
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("GPTC_REFERENCE_DIR", "/root/reference"))
-    ap.add_argument("--only", choices=["overlay", "reference"], default=None)
+    ap.add_argument("--reference", default=None, help="gpt.c source tree (default: GPTC_REFERENCE_DIR)")
     a = ap.parse_args()
-    print(build_all(a.reference, a.only))
+    ref = reference_dir(a.reference)
+    if ref is None:
+        sys.exit("no gpt.c source tree: pass --reference DIR or set GPTC_REFERENCE_DIR")
+    print(build_overlay(ref))

@@ -3,7 +3,8 @@ attention and with this repository's attention (the overlay build), on synthetic
 
     python gpt.c_b200/overlay/run_train_config.py [--steps 12] [--layers 12] [--out result.json] [--prepare DIR]
 
-Needs the two builds made by build_libgpt.py under oracle/_ref/ and a CUDA device.  A synthetic
+Needs this repository's build of gpt.c (build_libgpt.py, under overlay/_build/), the unmodified build
+beside the CPU checkers (oracle/build.py) and a CUDA device.  A synthetic
 checkpoint in the reference's format (train_gpt.c:201-287: 256-int header with magic 20240415,
 block size, vocab, layers, heads, width, shape-header length, steps; then (ndims, dims...) per
 tensor; then fp32 data in parameters() order) and a raw int32 token file (src/dataloader.c:44-80)
@@ -27,7 +28,7 @@ import numpy as np
 
 ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", ".."))
 BUILDS = {"reference_cuda_attention": os.path.join(ROOT, "oracle", "_ref", "gptc_reference"),
-          "sm100_attention": os.path.join(ROOT, "oracle", "_ref", "gptc_overlay")}
+          "sm100_attention": os.path.join(ROOT, "gpt.c_b200", "overlay", "_build", "gptc_overlay")}
 
 
 def write_checkpoint(path: str, n_layers: int, n_heads: int, n_embd: int, vocab: int, block: int, seed: int) -> None:
@@ -98,7 +99,7 @@ if __name__ == "__main__":
         sys.exit(0)
     missing = [k for k, d in BUILDS.items() if not os.path.exists(os.path.join(d, "train_gpt"))]
     if missing:
-        sys.exit(f"missing builds {missing}: run gpt.c_b200/overlay/build_libgpt.py where the reference tree is available")
+        sys.exit(f"missing builds {missing}: run gpt.c_b200/overlay/build_libgpt.py and oracle/build.py where the gpt.c tree is available")
     result = {"config": {"layers": a.layers, "heads": a.heads, "embd": a.embd, "batch": a.batch, "block": a.block,
                          "vocab": 50257, "steps": a.steps, "data": "synthetic uniform token ids, N(0,0.02) weights"}}
     with tempfile.TemporaryDirectory() as tmp:

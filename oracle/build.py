@@ -9,6 +9,13 @@ Two shared libraries are produced:
   This one is built only when the reference tree is present; the reference's own build system is
   not run and no reference source is copied.
 
+* ``oracle/_ref/gptc_reference/`` the whole unmodified reference (libgpt.so with its own CUDA attention
+  compiled for sm_100a, train_gpt, infer_gpt and the layer driver): the GPU baseline.  Compiled with the
+  package's gpt.c build recipe (``gpt.c_b200/overlay/build_libgpt.py``), again only when the reference
+  tree is present.
+
+The reference tree is taken from ``GPTC_REFERENCE_DIR`` or, failing that, from a directory ``reference``
+beside this repository.
 Run as ``python oracle/build.py``; ``build_all()`` is what the package-level build calls.
 The code is compiled for x86-64-v3 rather than for the building machine so the libraries still
 load on a different host CPU.
@@ -22,7 +29,8 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("GPTC_REFERENCE_DIR", "/root/reference")
+ROOT = os.path.dirname(HERE)
+REF_DIR = os.environ.get("GPTC_REFERENCE_DIR") or os.path.join(ROOT, "..", "reference")
 REF_OUT = os.path.join(HERE, "_ref")
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(REF_OUT, "libref_attention.so")
@@ -84,9 +92,30 @@ def build_reference(force: bool = False) -> str | None:
     return REF_SO
 
 
-def build_all(force: bool = False) -> dict:
-    return {"oracle": build_oracle(force), "reference": build_reference(force)}
+def build_reference_gptc(force: bool = False) -> str | None:
+    """The whole unmodified reference, CUDA attention included, as the GPU baseline.  None when the
+    reference tree is absent and no earlier build exists."""
+    out_dir = os.path.join(REF_OUT, "gptc_reference")
+    exe = os.path.join(out_dir, "layer_driver")
+    if not os.path.isdir(os.path.join(REF_DIR, "kernels", "src", "cuda")):
+        return out_dir if os.path.exists(exe) else None
+    if os.path.exists(exe) and not force:
+        return out_dir
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "gptc_b200_overlay_build", os.path.join(ROOT, "gpt.c_b200", "overlay", "build_libgpt.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build(os.path.abspath(REF_DIR), out_dir, overlay=False)
+
+
+def build_all(force: bool = False, gptc: bool = False) -> dict:
+    out = {"oracle": build_oracle(force), "reference": build_reference(force)}
+    if gptc:
+        out["reference_gptc"] = build_reference_gptc(force)
+    return out
 
 
 if __name__ == "__main__":
-    print(build_all(force="--force" in sys.argv))
+    print(build_all(force="--force" in sys.argv, gptc=True))

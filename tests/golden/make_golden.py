@@ -135,7 +135,8 @@ def make_config1_digest() -> None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("GPTC_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=oracle_build.REF_DIR,
+                    help="gpt.c source tree (default: GPTC_REFERENCE_DIR, else ../reference beside the repository)")
     args = ap.parse_args()
     oracle_build.build_all()
     if not oracle.have_reference():

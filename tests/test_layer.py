@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
-OVERLAY = os.path.join(ROOT, "oracle", "_ref", "gptc_overlay", "layer_driver")
+OVERLAY = os.path.join(ROOT, "gpt.c_b200", "overlay", "_build", "gptc_overlay", "layer_driver")
 REFERENCE = os.path.join(ROOT, "oracle", "_ref", "gptc_reference", "layer_driver")
 
 
@@ -65,7 +65,7 @@ def test_layer_forward_agrees_with_reference_cuda(tmp_path):
     assert np.abs(o_new - o_ref).max() < 2e-2  # TF32 operands on the reference side
 
 
-TRAIN_OVERLAY = os.path.join(ROOT, "oracle", "_ref", "gptc_overlay", "train_gpt")
+TRAIN_OVERLAY = os.path.join(ROOT, "gpt.c_b200", "overlay", "_build", "gptc_overlay", "train_gpt")
 TRAIN_REFERENCE = os.path.join(ROOT, "oracle", "_ref", "gptc_reference", "train_gpt")
 
 
