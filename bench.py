@@ -6,33 +6,50 @@
 One "step" is one forward + backward pass of the attention layer over one batch of synthetic
 input.  The workload is the GPT-2 124M block shape the metric is quoted on: B=8, T=1024, H=12,
 D=64, fp32 in/out, qkv and dout i.i.d. N(0,1) from a fixed seed.  With N > 1 (launched through
-torch.distributed.run, one rank per GPU) every rank processes its own batch of 8 -- the (batch,
-head) units are independent, so there is no collective on the data path and scaling is weak.
+torch.distributed.run, one rank per GPU) every rank processes its own batch of 8 for the headline
+value (weak scaling: the (batch, head) units are independent, there is no collective on the data
+path); the same line also carries a strong-scaling block in which ONE fixed workload is cut into
+contiguous batch slices, one per rank.
 
 Printed JSON line (rank 0):
   value      whole-job algorithmic TFLOP/s (6*B*H*T^2*D / 2 per pass, causal count) with inputs
-             resident in HBM, CUDA-event time, max over ranks
+             resident in HBM, CUDA-event time, max over ranks; the K-step timed loop is repeated
+             `repeats` times and value / ms_per_step are the median repeat (min and max beside it)
   e2e        the same metric through the C ABI with pinned HOST buffers: the H2D copy of qkv and
              dout and the D2H copy of out and dqkv are inside the timed region, every step; upload,
-             kernels and download run on three event-chained streams so consecutive steps overlap
+             kernels and download run on three event-chained streams so consecutive steps overlap.
+             e2e.copy_only is the same loop with the kernel calls left out: what the copies alone cost
   stage_us   launch duration of each of the four kernels, from a second pass over the same K steps
              with an event between the kernels (those events idle the GPU for a few microseconds
              each, so the headline pass runs without them)
   graph      the same K steps replayed from CUDA graphs (one per buffer set): no host in the loop
-  roofline   the dominant kernel (backward core) timed live with CUDA events
+  roofline   the dominant kernel (backward core) timed live with CUDA events, against the measured
+             burst cuBLAS bf16 rate (the kernel is timed in a millisecond burst)
   cpu_baseline  the reference's own CPU attention (OpenBLAS) on this box's host cores, rank 0, N=1
+  gpu_baseline  the reference's own CUDA attention (cuBLAS TF32 + SIMT kernels compiled for sm_100a,
+             unchanged) through its layer API on this GPU, and this repository's kernels through the
+             same layer API (allocation included), rank 0, N=1
+  train      GPT-2 124M training step through the unchanged train_gpt (12 layers, B=8, T=1024) with the
+             reference's kernels and with this repository's: ms per step and tokens/s, rank 0, N=1
+  strong     N > 1 (and N = 1 for the single-GPU time): GPT-2 XL shape B=64 H=25 forward+backward and
+             GPT-2 medium shape B=32 H=16 forward only, generated per batch entry from the seed, cut
+             into contiguous batch slices; per-rank kernel time (max over ranks), aggregate TFLOP/s
+             and efficiency against the whole workload on one GPU measured in the same run
 
 --impl reference times the reference's own CPU implementation of the path (compiled out of tree
-into oracle/_ref, else the plain-C port in oracle/) on the host cores, on a bounded sample per
-step, and prints the same line with "impl": "reference".
+into oracle/_ref, else the plain-C port in oracle/) on the host cores, one full B=8 pass per step,
+and prints the same line with "impl": "reference".
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import statistics
+import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -49,6 +66,7 @@ WORKLOADS = {
     "gpt2-xl-B64": {"B": 64, "T": 1024, "H": 25, "D": 64, "backward": True},
 }
 DEFAULT_WORKLOAD = "gpt2-124M-T1024"
+STRONG_WORKLOADS = ("gpt2-xl-B64", "gpt2-medium-fwd")  # cut over the ranks in the strong-scaling block
 WORKLOAD = dict(WORKLOADS[DEFAULT_WORKLOAD])
 SEED = 1234
 METRIC = "attn fwd+bwd TFLOP/s"
@@ -56,9 +74,12 @@ UNIT = "TFLOP/s"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 ROTATE = 4  # buffer sets cycled through so that a set is evicted from L2 before it is reused
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the
-# bench workload, from the ncu capture summarised under profiles/ (None until captured)
-BWD_CORE_DRAM_BYTES = 191820288  # profiles/ncu_full_attention_B8_T1024_H12.txt
+REPEATS = 10  # the K-step timed loop is run this many times; median and range are reported
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the bench
+# workload as captured with ncu (profiles/): shown for reference, never as this run's measurement
+BWD_CORE_DRAM_BYTES_PROFILED = {"bytes": 191820288, "source": "profiles/ncu_full_attention_B8_T1024_H12.txt"}
+REF_GPTC = os.path.join(ROOT, "oracle", "_ref", "gptc_reference")
+OUR_GPTC = os.path.join(ROOT, "gpt.c_b200", "overlay", "_build", "gptc_overlay")
 
 
 def flops_fwd(B, T, H, D):
@@ -190,23 +211,23 @@ def run_reference_arm(args):
     if rank != 0:
         return  # rank 0 alone measures the host cores
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
-    sample_b = 2
-    x, g = seeded_host_inputs(0, sample_b)
+    with_bwd = WORKLOAD["backward"]
+    x, g = seeded_host_inputs(0)  # the whole batch, every step: the same workload as our arm
     kind, run, info = cpu_attention_runner()
     for _ in range(args.warmup):
         run(x, g, H)
     times = [run(x, g, H) for _ in range(args.steps)]
     total = sum(times)
-    fl = (flops_fwd(sample_b, T, H, D) + flops_bwd(sample_b, T, H, D)) * args.steps
+    fl = (flops_fwd(B, T, H, D) + (flops_bwd(B, T, H, D) if with_bwd else 0.0)) * args.steps
     value = fl / total / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"causal attention fwd+bwd B={B} T={T} H={H} D={D} fp32 io", "sample_batch": sample_b,
-                   "seed": SEED},
+        "config": {"workload": f"causal attention fwd+bwd, fused qkv [B,T,3C] fp32 io, B={B} T={T} H={H} D={D} per GPU",
+                   "name": args.workload, "global_batch": B, "seq_len": T, "n_heads": H, "head_dim": D, "seed": SEED},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": kind,
-                         "sample": f"{sample_b} of {B} batch entries per step, fwd+bwd, {args.steps} steps",
+                         "sample": f"the full workload (all {B} batch entries) per step, fwd+bwd, {args.steps} steps",
                          "blas": info["blas"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -224,6 +245,68 @@ def measure_cpu_baseline():
     what = "the full workload" if sample_b == B else f"{sample_b} of {B} batch entries"
     return {"value": fl / secs / 1e12, "unit": UNIT, "cores": info["cores"], "kind": kind,
             "sample": f"one fwd+bwd pass of {what} (B={sample_b}), {secs:.2f} s", "blas": info["blas"]}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU baselines through gpt.c's own executables (rank 0, N=1)
+# ------------------------------------------------------------------------------------------------
+def measure_gpu_baseline(pairs: int = 10):
+    """The attention layer of gpt.c driven through its public API (include/attention.h) by the layer driver:
+    the unmodified reference build (its cuBLAS TF32 + SIMT attention, kernels/src/cuda/Attention.cu:170-324)
+    and this repository's build, same inputs, wall time per forward+backward pair with the allocations the
+    layer makes; `pooled` repeats the measurement with the default memory pool kept (see layer_driver.c)."""
+    import numpy as np
+
+    B, T, H, D = (WORKLOAD[k] for k in "BTHD")
+    C = H * D
+    out = {"unit": "ms per forward+backward pair through the layer API", "pairs": pairs,
+           "config": f"B={B} T={T} H={H} D={D}"}
+    exes = {"reference_cuda": os.path.join(REF_GPTC, "layer_driver"), "this_repo": os.path.join(OUR_GPTC, "layer_driver")}
+    missing = [k for k, e in exes.items() if not os.path.exists(e)]
+    if missing:
+        return {"unavailable": f"layer_driver builds missing: {missing}"}
+    with tempfile.TemporaryDirectory() as tmp:
+        x, g = seeded_host_inputs(0)
+        x.tofile(os.path.join(tmp, "x.bin"))
+        g.tofile(os.path.join(tmp, "g.bin"))
+        for name, exe in exes.items():
+            for mode in ("as_shipped", "pooled"):
+                cmd = [exe, "cuda", str(B), str(T), str(C), str(H), os.path.join(tmp, "x.bin"), os.path.join(tmp, "g.bin"),
+                       os.path.join(tmp, "o.bin"), os.path.join(tmp, "dx.bin"), str(pairs)]
+                if mode == "pooled":
+                    cmd.append("keep-pool")
+                try:
+                    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+                    m = re.search(r"mean_ms=([\d.]+)", res.stdout)
+                    out.setdefault(name, {})[mode] = float(m.group(1)) if (res.returncode == 0 and m) else None
+                    if res.returncode != 0 or not m:
+                        out[name][mode + "_error"] = (res.stdout + res.stderr)[-300:]
+                except Exception as e:  # a missing CUDA runtime for keep-pool, a timeout: report, do not fail the bench
+                    out.setdefault(name, {})[mode] = None
+                    out[name][mode + "_error"] = repr(e)[:300]
+    fl = flops_fwd(B, T, H, D) + flops_bwd(B, T, H, D)
+    for name in exes:
+        ms = out.get(name, {}).get("pooled")
+        if ms:
+            out[name]["tflops_pooled"] = fl / (ms * 1e-3) / 1e12
+    out["kernel_time_profiled"] = {"reference_cuda_us_per_pair": 2907.0,
+                                   "source": "profiles/reference_cuda_attention_layer_B8_T1024_H12.txt (ncu launch list)"}
+    return out
+
+
+def measure_train(steps: int = 8):
+    """Config 4: GPT-2 124M training step through the unchanged train_gpt, ms/step and tokens/s parsed from
+    its stdout (train_gpt.c:517), for the unmodified reference and for this repository's build."""
+    import importlib.util
+
+    path = os.path.join(ROOT, "gpt.c_b200", "overlay", "run_train_config.py")
+    spec = importlib.util.spec_from_file_location("gptc_b200_run_train_config", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    try:
+        return mod.run(steps=steps)
+    except Exception as e:
+        return {"unavailable": repr(e)[:300]}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -257,6 +340,23 @@ def bind_to_gpu_cpus(local_rank: int):
     return None
 
 
+def seeded_device_entries(dev, start: int, stop: int, T: int, H: int, D: int, with_bwd: bool):
+    """Batch entries [start, stop) of a fixed workload: entry b is drawn from a generator seeded with
+    (SEED, b), so every rank produces exactly the entries of its slice whatever the number of ranks."""
+    import torch
+
+    C = H * D
+    x = torch.empty((stop - start, T, 3 * C), device=dev)
+    g = torch.empty((stop - start, T, C), device=dev) if with_bwd else None
+    gen = torch.Generator(device=dev)
+    for i, b in enumerate(range(start, stop)):
+        gen.manual_seed(SEED * 100003 + b)
+        x[i].normal_(generator=gen)
+        if with_bwd:
+            g[i].normal_(generator=gen)
+    return x, g
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -275,6 +375,7 @@ def run_ours(args):
 
     pkg = entry.load_package()
     pkg.init()
+    shard = entry.load_submodule("shard")
     B, T, H, D = (WORKLOAD[k] for k in "BTHD")
     with_bwd = WORKLOAD["backward"]
     C = H * D
@@ -310,22 +411,17 @@ def run_ours(args):
                 pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H)
             return
         # staged variant: the same four kernels launched one by one with an event between them
-        if events is not None:
-            events[0].record(stream)
+        events[0].record(stream)
         pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_PREPARE_ONLY)
-        if events is not None:
-            events[1].record(stream)
+        events[1].record(stream)
         pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, pkg.FLAG_CORE_ONLY)
-        if events is not None:
-            events[2].record(stream)
+        events[2].record(stream)
         if with_bwd:
             pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_PREPARE_ONLY)
-        if events is not None:
-            events[3].record(stream)
+        events[3].record(stream)
         if with_bwd:
             pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, pkg.FLAG_CORE_ONLY)
-        if events is not None:
-            events[4].record(stream)
+        events[4].record(stream)
 
     def barrier():
         if world > 1:
@@ -339,6 +435,17 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed(fn, n):
+        """n calls of fn(i) between a barrier + synchronise on both sides; device time, max over ranks."""
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record(stream)
+        for i in range(n):
+            fn(i)
+        b.record(stream)
+        barrier()
+        return max_over_ranks(a.elapsed_time(b))
+
     # clock ramp (untimed, not counted as warm-up): the GPU idles at a low clock
     t_end = time.perf_counter() + (0.0 if args.no_ramp else 0.3)
     i = 0
@@ -350,33 +457,21 @@ def run_ours(args):
     # ---------------- device-resident timed region ----------------
     for i in range(args.warmup):
         step(i)
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    barrier()
     sampler.start()
-    t0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    t1.record(stream)
-    barrier()
-    ms_total = max_over_ranks(t0.elapsed_time(t1))
+    loop_ms = [timed(step, args.steps) for _ in range(args.repeats)]
+    ms_total = statistics.median(loop_ms)
     # Second timed pass over the same K steps with an event between the kernels: it gives the launch
     # duration of each kernel (the roofline uses the backward core's).  The events cost a few
     # microseconds of idle GPU each, which is why the headline pass above runs without them.
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    s0.record(stream)
-    for i in range(args.steps):
-        step(i, ev[i])
-    s1.record(stream)
-    barrier()
+    staged_ms_total = timed(lambda i: step(i, ev[i]), args.steps)
     clocks = sampler.stop()
-    staged_ms_total = max_over_ranks(s0.elapsed_time(s1))
     status = pkg.device_status()
     if status != 0:
         raise SystemExit(f"kernel status word {status}: a bounded wait ran out")
     stage_ms = [statistics.mean(ev[i][k].elapsed_time(ev[i][k + 1]) for i in range(args.steps)) for k in range(4)]
+    stage_med = [statistics.median(ev[i][k].elapsed_time(ev[i][k + 1]) for i in range(args.steps)) for k in range(4)]
 
     # ---------------- optional: the same steps replayed from CUDA graphs ----------------
     # For short sequences the four launches of a step take less GPU time than the host needs to issue
@@ -399,14 +494,7 @@ def run_ours(args):
         stream.wait_stream(side)
         for i in range(args.warmup):
             graphs[i % rotate].replay()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        g0.record(stream)
-        for i in range(args.steps):
-            graphs[i % rotate].replay()
-        g1.record(stream)
-        barrier()
-        graph_ms = max_over_ranks(g0.elapsed_time(g1))
+        graph_ms = timed(lambda i: graphs[i % rotate].replay(), args.steps)
         if pkg.device_status() != 0:
             raise SystemExit("kernel status word set during graph replay")
         graph_info = {"ms_per_step": graph_ms / args.steps}
@@ -421,7 +509,7 @@ def run_ours(args):
     comp_done = [torch.cuda.Event() for _ in range(rotate)]
     out_done = [torch.cuda.Event() for _ in range(rotate)]
 
-    def e2e_step(i):
+    def e2e_step(i, kernels=True):
         k = i % rotate
         s = sets[k]
         with torch.cuda.stream(s_in):
@@ -432,9 +520,10 @@ def run_ours(args):
             in_done[k].record(s_in)
         stream.wait_event(in_done[k])
         stream.wait_event(out_done[k])  # the download that last read this set's outputs
-        pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, stream=stream)
-        if with_bwd:
-            pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, stream=stream)
+        if kernels:
+            pkg.forward_into(s["x"], s["out"], None, s["lse"], s["saved"], H, stream=stream)
+            if with_bwd:
+                pkg.backward_into(s["saved"], s["out"], s["lse"], s["g"], s["dx"], s["scratch"], H, stream=stream)
         comp_done[k].record(stream)
         with torch.cuda.stream(s_out):
             s_out.wait_event(comp_done[k])
@@ -447,44 +536,53 @@ def run_ours(args):
         stream.wait_stream(s_in)
         stream.wait_stream(s_out)
 
-    for i in range(args.warmup):
-        e2e_step(i)
-    e2e_join()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    s_in.wait_event(e0)
-    for i in range(args.steps):
-        e2e_step(i)
-    e2e_join()
-    e1.record(stream)
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    def e2e_timed(kernels: bool) -> float:
+        for i in range(args.warmup):
+            e2e_step(i, kernels)
+        e2e_join()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        s_in.wait_event(e0)
+        for i in range(args.steps):
+            e2e_step(i, kernels)
+        e2e_join()
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    e2e_ms = e2e_timed(True)
+    e2e_copy_ms = e2e_timed(False)  # the same three streams and copies, kernel calls left out
+    if pkg.device_status() != 0:
+        raise SystemExit("kernel status word set during the end-to-end pass")
 
     flops_step = flops_fwd(B, T, H, D) + (flops_bwd(B, T, H, D) if with_bwd else 0.0)
-    value = flops_step * world * args.steps / (ms_total * 1e-3) / 1e12
-    e2e_value = flops_step * world * args.steps / (e2e_ms * 1e-3) / 1e12
+    to_tflops = lambda total_ms: flops_step * world * args.steps / (total_ms * 1e-3) / 1e12  # noqa: E731
+    value = to_tflops(ms_total)
+    e2e_value = to_tflops(e2e_ms)
     h2d = x_pin.numel() * 4 + (g_pin.numel() * 4 if with_bwd else 0)
     d2h = out_pin.numel() * 4 + (dx_pin.numel() * 4 if with_bwd else 0)
 
     peaks = load_peaks()
-    peak_tf = peaks["bf16_tflops_sustained"]
     ab = algorithmic_bytes(B, T, H, D)
     is_default = all(WORKLOAD[k] == WORKLOADS[DEFAULT_WORKLOAD][k] for k in WORKLOAD)
     if with_bwd:
         # dominant kernel: the backward core.  The tensor pipe really executes 15 passes per 4
         # algorithmic products: S is recomputed (5 products) and every product is three bf16 passes.
-        core_s, core_fl, core_bytes, passes = stage_ms[3] * 1e-3, flops_bwd(B, T, H, D), ab["bwd"], 15.0 / 4.0
+        core_s, core_fl, core_bytes, passes = stage_med[3] * 1e-3, flops_bwd(B, T, H, D), ab["bwd"], 15.0 / 4.0
         kernel_name = "attn_bwd_kernel (backward core)"
     else:
-        core_s, core_fl, core_bytes, passes = stage_ms[1] * 1e-3, flops_fwd(B, T, H, D), ab["fwd"], 3.0
+        core_s, core_fl, core_bytes, passes = stage_med[1] * 1e-3, flops_fwd(B, T, H, D), ab["fwd"], 3.0
         kernel_name = "attn_fwd_kernel (forward core)"
     achieved = core_fl / core_s / 1e12
+    peak_tf = peaks["bf16_tflops"]  # the kernel is timed alone in a millisecond burst: the burst figure applies
     roofline = {
         "kernel": kernel_name, "bound": "tensor", "achieved": achieved, "peak": peak_tf,
         "unit": "TFLOP/s", "frac": achieved / peak_tf,
-        "traffic": BWD_CORE_DRAM_BYTES if (with_bwd and is_default) else None,
-        "peak_source": peaks["source"] + " (cuBLAS bf16, sustained)",
+        "traffic": None,  # not captured in this run (ncu is never run inside the bench)
+        "traffic_profiled": BWD_CORE_DRAM_BYTES_PROFILED if (with_bwd and is_default) else None,
+        "peak_source": peaks["source"] + " (cuBLAS bf16, burst)",
+        "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"], "sustained_peak": peaks["bf16_tflops_sustained"],
         "launch_us": core_s * 1e6,
         "executed": {"tflops": achieved * passes, "frac": achieved * passes / peak_tf,
                      "passes_per_algorithmic_product": passes},
@@ -492,9 +590,73 @@ def run_ours(args):
                 "frac": core_bytes / core_s / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": core_bytes},
     }
 
-    cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_baseline = measure_cpu_baseline()
+    # ---------------- strong scaling: one fixed workload cut into contiguous batch slices ----------------
+    strong = None
+    if args.strong and is_default:
+        strong = {}
+        del sets[:]
+        torch.cuda.empty_cache()
+        for name in STRONG_WORKLOADS:
+            wl = WORKLOADS[name]
+            sB, sT, sH, sD, sbwd = wl["B"], wl["T"], wl["H"], wl["D"], wl["backward"]
+            fl_all = flops_fwd(sB, sT, sH, sD) + (flops_bwd(sB, sT, sH, sD) if sbwd else 0.0)
+
+            def run_slice(lo, hi, reps=args.steps):
+                """Kernel time (ms per pass) of batch entries [lo, hi) on this rank's GPU."""
+                n = hi - lo
+                if n == 0:
+                    return 0.0
+                x, g = seeded_device_entries(dev, lo, hi, sT, sH, sD, sbwd)
+                out = torch.empty((n, sT, sH * sD), device=dev)
+                lse = torch.empty((n, sH, sT), device=dev)
+                saved = torch.empty(pkg.saved_bytes(n, sT, sH, sD), device=dev, dtype=torch.uint8)
+                dx = torch.empty((n, sT, 3 * sH * sD), device=dev) if sbwd else None
+                scratch = torch.empty(pkg.backward_scratch_bytes(n, sT, sH, sD), device=dev, dtype=torch.uint8) if sbwd else None
+
+                def one(_i):
+                    pkg.forward_into(x, out, None, lse, saved, sH)
+                    if sbwd:
+                        pkg.backward_into(saved, out, lse, g, dx, scratch, sH)
+
+                for w in range(3):
+                    one(w)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for r in range(reps):
+                    one(r)
+                b.record(stream)
+                torch.cuda.synchronize()
+                del x, g, out, lse, saved, dx, scratch
+                torch.cuda.empty_cache()
+                return a.elapsed_time(b) / reps
+
+            lo, hi = shard.batch_slices(sB, world)[rank]
+            barrier()
+            ms_rank = run_slice(lo, hi)
+            ms_split = max_over_ranks(ms_rank)
+            # the whole workload on ONE GPU, in the same run (rank 0; the others wait at the barrier)
+            ms_single = run_slice(0, sB) if rank == 0 else 0.0
+            ms_single = max_over_ranks(ms_single)
+            barrier()
+            strong[name] = {
+                "B": sB, "T": sT, "H": sH, "D": sD, "passes": "fwd+bwd" if sbwd else "fwd",
+                "slices": shard.batch_slices(sB, world), "ms_per_pass_max_over_ranks": ms_split,
+                "tflops": fl_all / (ms_split * 1e-3) / 1e12,
+                "single_gpu_ms_per_pass": ms_single, "single_gpu_tflops": fl_all / (ms_single * 1e-3) / 1e12,
+                "efficiency": ms_single / (world * ms_split),
+            }
+        if pkg.device_status() != 0:
+            raise SystemExit("kernel status word set during the strong-scaling block")
+
+    cpu_baseline = gpu_baseline = train = None
+    if rank == 0 and world == 1:
+        if not args.no_cpu_baseline:
+            cpu_baseline = measure_cpu_baseline()
+        if is_default and args.gpu_baseline:
+            gpu_baseline = measure_gpu_baseline()
+        if is_default and args.train:
+            train = measure_train()
 
     if rank == 0:
         line = {
@@ -510,20 +672,30 @@ def run_ours(args):
                 "l2": f"{rotate} rotating buffer sets of {set_bytes / 1e6:.0f} MB each (> 126 MB L2 between reuses)",
                 "parallelism": f"batch shards on {world} GPU(s), no collective",
             },
+            "repeats": {"n": args.repeats, "ms_per_step_median": ms_total / args.steps,
+                        "ms_per_step_min": min(loop_ms) / args.steps, "ms_per_step_max": max(loop_ms) / args.steps,
+                        "value_min": to_tflops(max(loop_ms)), "value_max": to_tflops(min(loop_ms))},
             "pct_of_nominal_bf16_peak": 100.0 * value / (NOMINAL_BF16_TFLOPS * world),
-            "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops_sustained"] * world),
+            "pct_of_measured_bf16_peak": 100.0 * value / (peaks["bf16_tflops"] * world),
+            "pct_of_measured_sustained_bf16_peak": 100.0 * value / (peaks["bf16_tflops_sustained"] * world),
             "staged_pass_ms_per_step": staged_ms_total / args.steps,
             "stage_us": {"fwd_split": stage_ms[0] * 1e3, "fwd_core": stage_ms[1] * 1e3,
                          "bwd_prepare": stage_ms[2] * 1e3, "bwd_core": stage_ms[3] * 1e3},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": (4 if with_bwd else 2) * args.steps,
+                    "ms_per_step": e2e_ms / args.steps,
+                    "copy_only": {"ms_per_step": e2e_copy_ms / args.steps,
+                                  "host_gbs_per_direction": h2d * world / (e2e_copy_ms / args.steps * 1e-3) / 1e9,
+                                  "note": "the same three streams and copies with the kernel calls left out, all ranks at once"}},
+            "gpu_launches": (4 if with_bwd else 2) * args.steps,  # per K-step timed loop (each of the `repeats` loops)
             "host_cores_bound": cpu_affinity,
             "clocks": clocks,
             "graph": (graph_info | {"value": flops_step * world / (graph_info["ms_per_step"] * 1e-3) / 1e12,
                                     "unit": UNIT}) if graph_info else None,
             "roofline": roofline,
+            "strong": strong,
             "cpu_baseline": cpu_baseline,
+            "gpu_baseline": gpu_baseline,
+            "train": train,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -535,11 +707,19 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--repeats", type=int, default=REPEATS, help="how many times the K-step timed loop is run")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    ap.add_argument("--no-gpu-baseline", dest="gpu_baseline", action="store_false",
+                    help="skip the reference-CUDA / layer-API leg (rank 0, N=1)")
+    ap.add_argument("--no-train", dest="train", action="store_false",
+                    help="skip the GPT-2 124M train_gpt leg (rank 0, N=1)")
+    ap.add_argument("--no-strong", dest="strong", action="store_false", help="skip the strong-scaling block")
     ap.add_argument("--no-ramp", action="store_true", help="skip the untimed clock ramp (for profiler captures)")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="skip the extra pass that replays the steps from CUDA graphs (one per buffer set)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="profiler runs: headline and staged passes only (implies every --no-* leg)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD,
                     help="shape to run; the default is the one the metric is quoted on")
     args = ap.parse_args()
@@ -547,6 +727,11 @@ def main():
     WORKLOAD.update(WORKLOADS[args.workload])
     if args.warmup < 3:
         args.warmup = 3
+    if args.repeats < 1:
+        args.repeats = 1
+    if args.kernels_only:
+        args.no_cpu_baseline, args.gpu_baseline, args.train, args.strong, args.graph = True, False, False, False, False
+        args.repeats = 1
     if args.impl == "reference":
         if args.steps > 20:
             args.steps = 20  # each step is ~a second of host work; keep the arm within minutes

@@ -116,9 +116,15 @@ def build(ref: str, out_dir: str, overlay: bool) -> str:
 
     exe_srcs = {"train_gpt": os.path.join(ref, "train_gpt.c"), "infer_gpt": os.path.join(ref, "infer_gpt.c"),
                 "layer_driver": os.path.join(HERE, "layer_driver.c")}
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     for name, src in exe_srcs.items():
+        extra = []
+        if name == "layer_driver" and os.path.exists(os.path.join(cuda_home, "lib64", "libcudart.so")):
+            # the driver's keep-pool option sets an attribute of the device's default memory pool
+            extra = ["-DLAYER_DRIVER_CUDART", "-I", os.path.join(cuda_home, "include"), "-L", os.path.join(cuda_home, "lib64"),
+                     "-lcudart", "-Wl,-rpath," + os.path.join(cuda_home, "lib64")]
         run(["gcc", *host_flags, *defs, *inc, src, "-o", os.path.join(out_dir, name), lib, "-Wl,-rpath,$ORIGIN",
-             "-Wl,-rpath," + out_dir, "-lm", "-lgomp"])
+             "-Wl,-rpath," + out_dir, "-lm", "-lgomp", *extra])
     return out_dir
 
 

@@ -74,6 +74,37 @@ def run_build(build_dir: str, ckpt: str, tokens: str, batch: int, block: int, lo
     return res.returncode, [(int(s), float(l), float(ms)) for s, l, ms in steps], res.stdout[-1500:] + res.stderr[-1500:]
 
 
+def run(steps: int = 12, layers: int = 12, heads: int = 12, embd: int = 768, batch: int = 8, block: int = 1024) -> dict:
+    """Runs both builds on the same synthetic checkpoint and token file; returns the result dictionary."""
+    missing = [k for k, d in BUILDS.items() if not os.path.exists(os.path.join(d, "train_gpt"))]
+    if missing:
+        raise RuntimeError(f"missing builds {missing}: run gpt.c_b200/overlay/build_libgpt.py and oracle/build.py "
+                           "where the gpt.c tree is available")
+    result = {"config": {"layers": layers, "heads": heads, "embd": embd, "batch": batch, "block": block,
+                         "vocab": 50257, "steps": steps, "data": "synthetic uniform token ids, N(0,0.02) weights"}}
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt, tok = os.path.join(tmp, "ckpt.bin"), os.path.join(tmp, "tokens.bin")
+        write_checkpoint(ckpt, layers, heads, embd, 50257, block, seed=1234)
+        write_tokens(tok, steps, batch, block, 50257, seed=4321)
+        for name, d in BUILDS.items():
+            rc, log, tail = run_build(d, ckpt, tok, batch, block, os.path.join(tmp, "logs_" + name))
+            entry = {"returncode": rc, "losses": [l for _, l, _ in log], "step_ms": [ms for _, _, ms in log]}
+            timed = [ms for s, _, ms in log if s >= 3]
+            if timed:
+                entry["median_step_ms"] = statistics.median(timed)
+                entry["tokens_per_s"] = batch * block / (entry["median_step_ms"] * 1e-3)
+            if rc != 0 or not log:
+                entry["output_tail"] = tail
+            result[name] = entry
+    ref, new = result["reference_cuda_attention"], result["sm100_attention"]
+    if ref.get("losses") and new.get("losses"):
+        n = min(len(ref["losses"]), len(new["losses"]))
+        result["max_loss_difference"] = max(abs(x - y) for x, y in zip(ref["losses"][:n], new["losses"][:n]))
+    if "tokens_per_s" in ref and "tokens_per_s" in new:
+        result["speedup_tokens_per_s"] = new["tokens_per_s"] / ref["tokens_per_s"]
+    return result
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=12)
@@ -97,31 +128,10 @@ if __name__ == "__main__":
                   f"--block-size={a.block}", f"--load-checkpoint={ckpt}", "--device=cuda", "--lr=3e-4",
                   f"--log-dir={os.path.join(a.prepare, 'logs_' + name)}")
         sys.exit(0)
-    missing = [k for k, d in BUILDS.items() if not os.path.exists(os.path.join(d, "train_gpt"))]
-    if missing:
-        sys.exit(f"missing builds {missing}: run gpt.c_b200/overlay/build_libgpt.py and oracle/build.py where the gpt.c tree is available")
-    result = {"config": {"layers": a.layers, "heads": a.heads, "embd": a.embd, "batch": a.batch, "block": a.block,
-                         "vocab": 50257, "steps": a.steps, "data": "synthetic uniform token ids, N(0,0.02) weights"}}
-    with tempfile.TemporaryDirectory() as tmp:
-        ckpt, tok = os.path.join(tmp, "ckpt.bin"), os.path.join(tmp, "tokens.bin")
-        write_checkpoint(ckpt, a.layers, a.heads, a.embd, 50257, a.block, seed=1234)
-        write_tokens(tok, a.steps, a.batch, a.block, 50257, seed=4321)
-        for name, d in BUILDS.items():
-            rc, steps, tail = run_build(d, ckpt, tok, a.batch, a.block, os.path.join(tmp, "logs_" + name))
-            entry = {"returncode": rc, "losses": [l for _, l, _ in steps], "step_ms": [ms for _, _, ms in steps]}
-            timed = [ms for s, _, ms in steps if s >= 3]
-            if timed:
-                entry["median_step_ms"] = statistics.median(timed)
-                entry["tokens_per_s"] = a.batch * a.block / (entry["median_step_ms"] * 1e-3)
-            if rc != 0 or not steps:
-                entry["output_tail"] = tail
-            result[name] = entry
-    ref, new = result["reference_cuda_attention"], result["sm100_attention"]
-    if ref.get("losses") and new.get("losses"):
-        n = min(len(ref["losses"]), len(new["losses"]))
-        result["max_loss_difference"] = max(abs(x - y) for x, y in zip(ref["losses"][:n], new["losses"][:n]))
-    if "tokens_per_s" in ref and "tokens_per_s" in new:
-        result["speedup_tokens_per_s"] = new["tokens_per_s"] / ref["tokens_per_s"]
+    try:
+        result = run(a.steps, a.layers, a.heads, a.embd, a.batch, a.block)
+    except RuntimeError as e:
+        sys.exit(str(e))
     text = json.dumps(result)
     print(text)
     if a.out:
