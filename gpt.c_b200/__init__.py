@@ -33,6 +33,7 @@ SIGNATURES = {
     "attn_sm100_forward": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 5 + [_c.c_void_p]),
     "attn_sm100_backward": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 5 + [_c.c_void_p]),
     "attn_sm100_forward_static": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 4 + [_c.c_void_p]),
+    "attn_sm100_static_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "attn_sm100_selftest_wait_limit": (_c.c_int, [_c.c_uint, _c.c_void_p]),
     "attn_sm100_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "attn_sm100_strerror": (_c.c_char_p, [_c.c_int]),
@@ -97,6 +98,15 @@ def device_status(clear: bool = True) -> int:
     rc = lib().attn_sm100_device_status(ctypes.byref(st), 1 if clear else 0)
     if rc not in (0, -6):
         raise AttnError(rc, "attn_sm100_device_status")
+    return st.value
+
+
+def static_status(clear: bool = True) -> int:
+    """The same for the status word of attn_sm100_forward_static (a separate word inside the library)."""
+    st = ctypes.c_int(0)
+    rc = lib().attn_sm100_static_status(ctypes.byref(st), 1 if clear else 0)
+    if rc not in (0, -6):
+        raise AttnError(rc, "attn_sm100_static_status")
     return st.value
 
 

@@ -8,6 +8,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/attn_sm100.h"
 
 namespace {
@@ -15,11 +18,12 @@ namespace {
 constexpr int kMaxDevices = 64;
 
 struct DeviceState {
-    bool ready = false;
+    std::atomic<bool> ready{false};  // set last, under g_init_lock; read without it on the fast path
     int *status = nullptr;  // device word written by kernels whose bounded waits run out
     int num_sms = 0;        // the persistent backward kernel runs one CTA per SM
 };
 DeviceState g_dev[kMaxDevices];
+std::mutex g_init_lock;  // per-device set-up may be entered by several host threads at once
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -68,7 +72,7 @@ int current_device_state(DeviceState **out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return ATTN_ERR_DEVICE;
-    if (!g_dev[dev].ready) {
+    if (!g_dev[dev].ready.load(std::memory_order_acquire)) {
         const int rc = attn_sm100_init();
         if (rc != ATTN_OK) return rc;
     }
@@ -130,7 +134,9 @@ int attn_sm100_init(void) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return ATTN_ERR_DEVICE;
-    if (g_dev[dev].ready) return ATTN_OK;
+    if (g_dev[dev].ready.load(std::memory_order_acquire)) return ATTN_OK;
+    std::lock_guard<std::mutex> guard(g_init_lock);
+    if (g_dev[dev].ready.load(std::memory_order_relaxed)) return ATTN_OK;
 
     int major = 0;
     e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
@@ -156,7 +162,7 @@ int attn_sm100_init(void) {
     if ((e = cudaMalloc(&st, sizeof(int))) != cudaSuccess) return (int)e;
     if ((e = cudaMemset(st, 0, sizeof(int))) != cudaSuccess) return (int)e;
     g_dev[dev].status = st;
-    g_dev[dev].ready = true;
+    g_dev[dev].ready.store(true, std::memory_order_release);
     return ATTN_OK;
 }
 

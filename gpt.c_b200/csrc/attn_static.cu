@@ -14,6 +14,8 @@
 // overlap on the GPU (different streams, different host threads) race on it.
 #include "attn_internal.h"
 
+#include <mutex>
+
 #include "../../include/attn_sm100.h"
 
 namespace {
@@ -31,6 +33,7 @@ struct StaticState {
     int *status = nullptr;
 };
 StaticState g_state[kMaxDevices];
+std::mutex g_setup_lock;  // set-up is per device and may be entered by several host threads at once
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -41,6 +44,7 @@ EncodeTiledFn g_encode_static = nullptr;
 // g_static_status are only stand-ins for the device objects: a kernel must be given the address
 // cudaGetSymbolAddress returns, never &g_static_scratch itself.
 int setup_device(int dev) {
+    std::lock_guard<std::mutex> guard(g_setup_lock);
     StaticState &st = g_state[dev];
     if (st.ready) return ATTN_OK;
     int major = 0;
@@ -106,4 +110,22 @@ extern "C" int attn_sm100_forward_static(const float *qkv, float *out, float *ls
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return (int)cudaErrorInvalidValue;
     return (int)attn::launch_fast_forward(map_x, nullptr, nullptr, out, nullptr, lse, B, T, H, st.status, s);
+}
+
+
+// The status word of this entry point on the current device: the kernels above write it when a bounded
+// wait runs out.  It is a word inside the library image, read and cleared with symbol copies, so this
+// call allocates nothing either.
+extern "C" int attn_sm100_static_status(int *status, int clear) {
+    if (!status) return ATTN_ERR_NULL;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemcpyFromSymbol(status, g_static_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (clear && *status != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_static_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    return *status == 0 ? ATTN_OK : ATTN_ERR_KERNEL;
 }

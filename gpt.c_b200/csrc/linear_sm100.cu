@@ -742,7 +742,8 @@ int linear_sm100_backward(const float *dy, const float *x, const float *w, float
     const int np = (N + 31) / 32 * 32;
     if ((long long)M * np > 0x7fffffffLL) return ATTN_ERR_SHAPE;
     if (padded && !scratch) return ATTN_ERR_NULL;
-    if ((!padded && !aligned16(dy)) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) ||
+    // dy itself must start on a 16-byte boundary in both cases: the padding kernel reads it in 16-byte words
+    if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) ||
         (!padded && !aligned16(db)) || !aligned16(scratch))
         return ATTN_ERR_ALIGN;
     int *status = nullptr;

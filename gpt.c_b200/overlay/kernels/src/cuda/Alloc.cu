@@ -12,6 +12,7 @@
 #include <cuda/cuda_common.h>
 #include <cuda/runtime.cuh>
 #include <cuda/Alloc.h>
+#include "attn_planes.h"
 
 static void keep_freed_memory_once(void) {
     static int done = 0;
@@ -36,6 +37,7 @@ void *alloc_cuda(const size_t size) {
 
 void free_cuda(void *ptr) {
     if (ptr == NULL) return;
+    overlay_planes_forget(ptr);  // bf16 planes offered for this tensor die with it (its address will be reused)
     cudaCheck(cudaFreeAsync(ptr, get_cuda_stream()));
 }
 

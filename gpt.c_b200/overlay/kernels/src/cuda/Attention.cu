@@ -43,6 +43,8 @@ void attention_forward_cuda_kernel(const tensor_t *input, const tensor_t *mask, 
             cache[0]->t = (float *)planes;
             flags = ATTN_FLAG_CORE_ONLY;
         }
+    } else {
+        overlay_planes_forget(NULL);  // planes are only made for head size 64: nobody will take a pending offer
     }
     attn_check(attn_sm100_forward(input->t, output->t, cache[2]->t, cache[1]->t, cache[0]->t, B, T, n_heads, D, flags,
                                   (void *)stream),

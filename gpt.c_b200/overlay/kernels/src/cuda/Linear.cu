@@ -44,6 +44,15 @@ extern "C" void *overlay_planes_take(const float *y, size_t bytes) {
     return p;
 }
 
+extern "C" void overlay_planes_forget(const void *y) {
+    if (!g_offer_planes || (y != NULL && (const void *)g_offer_y != y)) return;
+    void *p = g_offer_planes;
+    g_offer_y = NULL;
+    g_offer_planes = NULL;
+    g_offer_bytes = 0;
+    free_cuda(p);  // stream ordered; the slot is already empty, so the nested call finds nothing to forget
+}
+
 // ---- fallback pieces for shapes outside the tensor-core kernels ----
 __global__ void overlay_add_bias_kernel(float *y, const float *bias, size_t rows, int cols) {
     const size_t n = rows * (size_t)cols;

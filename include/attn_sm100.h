@@ -137,14 +137,27 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
  *     i.e. B*T*3*H*D <= 4,194,304 elements; larger problems return ATTN_ERR_STATIC_CAPACITY.
  *   - No cudaMalloc / cudaFree / allocating library call is made, not even on first use.  The first
  *     call on each device resolves the device address of the array (cudaGetSymbolAddress) and raises
- *     the kernel's shared-memory limit; make that first call before starting any stream capture.
+ *     the kernel's shared-memory limit.  With CUDA's lazy module loading that first call is also the
+ *     moment the driver loads this library's code onto the device and reserves the array there, which
+ *     can take as long as an allocation: make the first call per device at start-up, and before
+ *     starting any stream capture.
  *   - All calls on a device share the array and it keeps the previous call's contents.  Each call
  *     rewrites every byte it reads, so nothing needs clearing, but calls that overlap on the GPU
  *     (other streams or threads) race on it: serialise them.
- *   - Kernel status for this path is separate from attn_sm100_device_status.
+ *   - Kernel status for this path is separate from attn_sm100_device_status: read it with
+ *     attn_sm100_static_status.
  */
 #define ATTN_STATIC_SCRATCH_BYTES (16u << 20)
 int attn_sm100_forward_static(const float *qkv, float *out, float *lse, int B, int T, int H, int D, void *stream);
+
+/*
+ * Status word of attn_sm100_forward_static on the current device (no counterpart in the reference).
+ * Synchronises the device; *status receives 0, or a code >= 1000 naming the bounded wait that ran out
+ * inside a kernel launched by attn_sm100_forward_static (its out / lse are then not valid).  When `clear`
+ * is non-zero the word is reset.  The word lives inside the library image like the scratch array, so this
+ * call allocates nothing.  Returns ATTN_OK, ATTN_ERR_KERNEL when *status != 0, or a cudaError_t.
+ */
+int attn_sm100_static_status(int *status, int clear);
 
 /*
  * Failure-path self-test (no counterpart in the reference, which has no bounded waits): launches a

@@ -53,7 +53,9 @@ size_t linear_sm100_backward_scratch_bytes(int M, int N, int K);
  * db[N]    += column sums of dy            (accumulated; db may be NULL)
  * dx or dw may be NULL (not both): that product is skipped, e.g. dx for a layer whose input needs no
  * gradient.  scratch: linear_sm100_backward_scratch_bytes(M, N, K) bytes, 16-byte aligned (NULL when 0).
- * Requirements: K % 32 == 0; else ATTN_ERR_UNSUPPORTED.
+ * Requirements: K % 32 == 0; else ATTN_ERR_UNSUPPORTED.  dy, x, w, dx, dw and scratch start on 16-byte
+ * boundaries (dy too when N is not a multiple of 4: only its later rows are unaligned then); else
+ * ATTN_ERR_ALIGN.
  * dw and db are built from fp32 additions whose order is not fixed (split over M): results can differ
  * in the last bits between runs.
  */

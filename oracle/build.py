@@ -9,6 +9,9 @@ Two shared libraries are produced:
   This one is built only when the reference tree is present; the reference's own build system is
   not run and no reference source is copied.
 
+* ``oracle/_ref/libref_ops.so`` from the reference's CPU kernels either side of the attention layer
+  (``kernels/src/cpu/{Linear,LayerNorm,CrossEntropyLoss,AdamW,GeLU}.c``) plus ``oracle/ref_ops_driver.c``,
+  the same way: they pin the numpy restatements in ``oracle/ops_oracle.py``.
 * ``oracle/_ref/gptc_reference/`` the whole unmodified reference (libgpt.so with its own CUDA attention
   compiled for sm_100a, train_gpt, infer_gpt and the layer driver): the GPU baseline.  Compiled with the
   package's gpt.c build recipe (``gpt.c_b200/overlay/build_libgpt.py``), again only when the reference
@@ -34,6 +37,7 @@ REF_DIR = os.environ.get("GPTC_REFERENCE_DIR") or os.path.join(ROOT, "..", "refe
 REF_OUT = os.path.join(HERE, "_ref")
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(REF_OUT, "libref_attention.so")
+REF_OPS_SO = os.path.join(REF_OUT, "libref_ops.so")
 
 CFLAGS = ["-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-Wall", "-Wno-unused-result"]
 
@@ -92,6 +96,29 @@ def build_reference(force: bool = False) -> str | None:
     return REF_SO
 
 
+def build_reference_ops(force: bool = False) -> str | None:
+    """Compile the reference CPU kernels of Linear, LayerNorm, cross-entropy, AdamW and GELU out of tree."""
+    srcs = [os.path.join(REF_DIR, "kernels/src/cpu", f + ".c") for f in ("Linear", "LayerNorm", "CrossEntropyLoss", "AdamW", "GeLU")]
+    srcs.append(os.path.join(REF_DIR, "kernels/src/cpu/Alloc.c"))
+    if not all(os.path.exists(s) for s in srcs):
+        return REF_OPS_SO if os.path.exists(REF_OPS_SO) else None
+    blas = find_openblas()
+    if blas is None:
+        return None
+    lib, scipy_prefix = blas
+    driver = os.path.join(HERE, "ref_ops_driver.c")
+    if not force and _newer(REF_OPS_SO, srcs + [driver, os.path.join(HERE, "cblas.h")]):
+        return REF_OPS_SO
+    os.makedirs(REF_OUT, exist_ok=True)
+    cmd = ["gcc", *CFLAGS, "-Wno-unknown-pragmas", "-Wno-attributes", "-Wno-discarded-qualifiers", "-Wno-unused-variable",
+           "-I", HERE, "-I", os.path.join(REF_DIR, "include"), "-I", os.path.join(REF_DIR, "kernels/src")]
+    if scipy_prefix:
+        cmd.append("-DREF_BLAS_SCIPY")
+    cmd += [driver, *srcs, "-o", REF_OPS_SO, lib, "-Wl,-rpath," + os.path.dirname(lib), "-lm"]
+    subprocess.check_call(cmd)
+    return REF_OPS_SO
+
+
 def build_reference_gptc(force: bool = False) -> str | None:
     """The whole unmodified reference, CUDA attention included, as the GPU baseline.  None when the
     reference tree is absent and no earlier build exists."""
@@ -111,7 +138,7 @@ def build_reference_gptc(force: bool = False) -> str | None:
 
 
 def build_all(force: bool = False, gptc: bool = False) -> dict:
-    out = {"oracle": build_oracle(force), "reference": build_reference(force)}
+    out = {"oracle": build_oracle(force), "reference": build_reference(force), "reference_ops": build_reference_ops(force)}
     if gptc:
         out["reference_gptc"] = build_reference_gptc(force)
     return out

@@ -117,3 +117,117 @@ def reference_run(x: np.ndarray, dout: np.ndarray | None, n_heads: int, threads:
 def reference_info() -> dict:
     lib = _load_ref()
     return {"threads": lib.ref_get_num_threads(), "blas": lib.ref_blas_config().decode(errors="replace")}
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's own CPU kernels of Linear, LayerNorm, cross-entropy, AdamW and GELU
+# (oracle/_ref/libref_ops.so, compiled out of tree by oracle/build.py with oracle/ref_ops_driver.c)
+# ---------------------------------------------------------------------------------------------
+REF_OPS_SO = os.path.join(HERE, "_ref", "libref_ops.so")
+_ref_ops = None
+
+
+def have_reference_ops() -> bool:
+    return os.path.exists(REF_OPS_SO)
+
+
+def _c(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+class ReferenceOps:
+    """numpy in, numpy out; in/out buffers of the kernels are passed as copies and returned."""
+
+    def __init__(self):
+        lib = ctypes.CDLL(REF_OPS_SO)
+        for name in ("ref_linear_forward", "ref_linear_backward", "ref_layernorm_forward", "ref_layernorm_backward",
+                     "ref_xent_forward", "ref_xent_backward", "ref_adamw_step", "ref_gelu_forward", "ref_gelu_backward"):
+            getattr(lib, name).restype = ctypes.c_int
+        self.lib = lib
+
+    @staticmethod
+    def _ok(rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} returned {rc}")
+
+    def linear_forward(self, x, w, b=None):
+        x, w = _c(x), _c(w)
+        b = None if b is None else _c(b)
+        M, K = x.shape
+        N = w.shape[0]
+        y = np.empty((M, N), np.float32)
+        self._ok(self.lib.ref_linear_forward(_p(x), _p(w), _p(b), _p(y), M, N, K), "ref_linear_forward")
+        return y
+
+    def linear_backward(self, dy, x, w, dw0, db0=None):
+        dy, x, w = _c(dy), _c(x), _c(w)
+        M, N = dy.shape
+        K = x.shape[1]
+        dx = np.empty((M, K), np.float32)
+        dw = _c(dw0).copy()
+        db = None if db0 is None else _c(db0).copy()
+        self._ok(self.lib.ref_linear_backward(_p(dy), _p(x), _p(w), _p(dx), _p(dw), _p(db), M, N, K), "ref_linear_backward")
+        return dx, dw, db
+
+    def layernorm_forward(self, x, w, b, eps):
+        x, w = _c(x), _c(w)
+        b = None if b is None else _c(b)
+        rows, C = x.shape
+        y, mean, rstd = np.empty((rows, C), np.float32), np.empty(rows, np.float32), np.empty(rows, np.float32)
+        self._ok(self.lib.ref_layernorm_forward(_p(x), _p(w), _p(b), ctypes.c_float(eps), _p(y), _p(mean), _p(rstd), rows, C),
+                 "ref_layernorm_forward")
+        return y, mean, rstd
+
+    def layernorm_backward(self, dy, x, mean, rstd, w, dw0, db0, dx0):
+        dy, x, mean, rstd, w = _c(dy), _c(x), _c(mean), _c(rstd), _c(w)
+        rows, C = x.shape
+        dw, dx = _c(dw0).copy(), _c(dx0).copy()
+        db = None if db0 is None else _c(db0).copy()
+        self._ok(self.lib.ref_layernorm_backward(_p(dy), _p(x), _p(mean), _p(rstd), _p(w), _p(dw), _p(db), _p(dx), rows, C),
+                 "ref_layernorm_backward")
+        return dw, db, dx
+
+    def xent_forward(self, logits, targets):
+        logits, targets = _c(logits), _c(targets)
+        rows, C = logits.shape
+        logsm, loss = np.empty((rows, C), np.float32), np.zeros(1, np.float32)
+        self._ok(self.lib.ref_xent_forward(_p(logits), _p(targets), _p(logsm), _p(loss), rows, C), "ref_xent_forward")
+        return logsm, float(loss[0])
+
+    def xent_backward(self, g, targets, logsm, dout0):
+        g, targets, logsm = _c(g), _c(targets), _c(logsm)
+        rows, C = logsm.shape
+        dout = _c(dout0).copy()
+        self._ok(self.lib.ref_xent_backward(_p(g), _p(targets), _p(logsm), _p(dout), rows, C), "ref_xent_backward")
+        return dout
+
+    def adamw_step(self, p, g, m, v, lr, b1, b2, wd, eps, step):
+        p, m, v = _c(p).copy(), _c(m).copy(), _c(v).copy()
+        g = _c(g)
+        f = ctypes.c_float
+        self._ok(self.lib.ref_adamw_step(_p(p), _p(g), _p(m), _p(v), p.size, f(lr), f(b1), f(b2), f(wd), f(eps), int(step)),
+                 "ref_adamw_step")
+        return p, m, v
+
+    def gelu_forward(self, x):
+        x = _c(x)
+        y = np.empty_like(x)
+        self._ok(self.lib.ref_gelu_forward(_p(x), _p(y), x.size), "ref_gelu_forward")
+        return y
+
+    def gelu_backward(self, g, x):
+        g, x = _c(g), _c(x)
+        dx = np.empty_like(x)
+        self._ok(self.lib.ref_gelu_backward(_p(g), _p(x), _p(dx), x.size), "ref_gelu_backward")
+        return dx
+
+
+def reference_ops() -> ReferenceOps:
+    global _ref_ops
+    if _ref_ops is None:
+        _ref_ops = ReferenceOps()
+    return _ref_ops

@@ -133,6 +133,53 @@ def make_config1_digest() -> None:
     print("config1_digest: out sum %.6f dx sum %.6f" % (s1, d1))
 
 
+def ops_inputs():
+    """Seeded inputs of the fixtures of the kernels either side of the attention layer (small shapes with
+    ragged sizes; the tests recompute the restatements on the same inputs)."""
+    rng = np.random.default_rng(20240415)
+    M, N, K = 37, 50, 24
+    rows, C = 29, 40
+    d = {
+        "lin_x": rng.standard_normal((M, K), dtype=np.float32), "lin_w": (rng.standard_normal((N, K), dtype=np.float32) * 0.1).astype(np.float32),
+        "lin_b": rng.standard_normal(N, dtype=np.float32), "lin_dy": rng.standard_normal((M, N), dtype=np.float32),
+        "lin_dw0": rng.standard_normal((N, K), dtype=np.float32), "lin_db0": rng.standard_normal(N, dtype=np.float32),
+        "ln_x": (rng.standard_normal((rows, C)) * 1.7 + 0.3).astype(np.float32), "ln_w": (1.0 + 0.1 * rng.standard_normal(C)).astype(np.float32),
+        "ln_b": (0.1 * rng.standard_normal(C)).astype(np.float32), "ln_dy": rng.standard_normal((rows, C)).astype(np.float32),
+        "ln_dw0": rng.standard_normal(C).astype(np.float32), "ln_db0": rng.standard_normal(C).astype(np.float32),
+        "ln_dx0": rng.standard_normal((rows, C)).astype(np.float32),
+        "ce_logits": (rng.standard_normal((rows, 101)) * 3.0).astype(np.float32), "ce_targets": rng.integers(0, 101, size=rows).astype(np.float32),
+        "ce_g": rng.standard_normal(rows).astype(np.float32), "ce_d0": (rng.standard_normal((rows, 101)) * 0.01).astype(np.float32),
+        "ad_p": (rng.standard_normal(1003) * 0.05).astype(np.float32), "ad_g": (rng.standard_normal(1003) * 0.01).astype(np.float32),
+        "ad_m": (rng.standard_normal(1003) * 0.001).astype(np.float32), "ad_v": (np.abs(rng.standard_normal(1003)) * 1e-4).astype(np.float32),
+        "ge_x": (rng.standard_normal(777) * 2.5).astype(np.float32), "ge_g": rng.standard_normal(777).astype(np.float32),
+    }
+    return d
+
+
+def make_ops() -> None:
+    """One fixture per kernel either side of the layer, produced by the reference's own CPU kernels."""
+    ref = oracle.reference_ops()
+    d = ops_inputs()
+    out = dict(d)
+    out["lin_y"] = ref.linear_forward(d["lin_x"], d["lin_w"], d["lin_b"])
+    out["lin_dx"], out["lin_dw"], out["lin_db"] = ref.linear_backward(d["lin_dy"], d["lin_x"], d["lin_w"], d["lin_dw0"], d["lin_db0"])
+    out["ln_y"], out["ln_mean"], out["ln_rstd"] = ref.layernorm_forward(d["ln_x"], d["ln_w"], d["ln_b"], 1e-5)
+    out["ln_dw"], out["ln_db"], out["ln_dx"] = ref.layernorm_backward(d["ln_dy"], d["ln_x"], out["ln_mean"], out["ln_rstd"], d["ln_w"],
+                                                                    d["ln_dw0"], d["ln_db0"], d["ln_dx0"])
+    out["ce_logsm"], loss = ref.xent_forward(d["ce_logits"], d["ce_targets"])
+    out["ce_loss"] = np.float32(loss)
+    out["ce_dout_zero"] = ref.xent_backward(d["ce_g"], d["ce_targets"], out["ce_logsm"], np.zeros_like(d["ce_d0"]))
+    out["ce_dout_d0"] = ref.xent_backward(d["ce_g"], d["ce_targets"], out["ce_logsm"], d["ce_d0"])
+    p, m, v = d["ad_p"], d["ad_m"], d["ad_v"]
+    for step in (1, 2, 3):
+        p, m, v = ref.adamw_step(p, d["ad_g"], m, v, 3e-4, 0.9, 0.999, 0.01, 1e-8, step)
+    out["ad_p3"], out["ad_m3"], out["ad_v3"] = p, m, v
+    out["ge_y"] = ref.gelu_forward(d["ge_x"])
+    out["ge_dx"] = ref.gelu_backward(d["ge_g"], d["ge_x"])
+    np.savez(os.path.join(HERE, "ops_cases.npz"), **out)
+    print("ops_cases: %d arrays" % len(out))
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=oracle_build.REF_DIR,
@@ -144,3 +191,5 @@ if __name__ == "__main__":
     make_ref_selfattn(args.reference)
     make_seeded()
     make_config1_digest()
+    if oracle.have_reference_ops():
+        make_ops()

@@ -1,4 +1,5 @@
-"""Parity of the AdamW step (include/adamw_sm100.h) against a numpy restatement of the reference's update
+"""Parity of the AdamW step (include/adamw_sm100.h) against the numpy restatement of the reference's update in
+oracle/ops_oracle.py, pinned to the reference's own CPU kernel by tests/test_ops_oracle.py
 (kernels/src/cuda/AdamW.cu:13-57, same formula as kernels/src/cpu/AdamW.c): decoupled weight decay, moments
 by lerp(a, b, w) = fma(w, b, fma(-w, a, a)), bias corrections as multiplications.  The restatement runs in
 float64 with a rounding to float32 after every operation the kernel rounds at, so the results agree to one
@@ -10,26 +11,11 @@ import numpy as np
 import pytest
 
 torch = pytest.importorskip("torch")
+from oracle import ops_oracle as ops  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
 f32 = np.float32
-
-
-def ref_step(p, g, m, v, lr, b1, b2, wd, eps, step):
-    p, g, m, v = (a.astype(np.float64) for a in (p, g, m, v))
-    # the kernel receives the hyper-parameters as float32 (1 - 0.999f differs from 0.001 by 1e-5 relative)
-    lr, b1, b2, wd, eps = (np.float64(f32(a)) for a in (lr, b1, b2, wd, eps))
-    r = lambda a: a.astype(f32).astype(np.float64)  # noqa: E731
-    p = r(p - r(r(f32(lr) * f32(wd)) * p))
-    m = r(b1 * m + r(-b1 * g + g))
-    gg = r(g * g)
-    v = r(b2 * v + r(-b2 * gg + gg))
-    c1 = np.float64(f32(1.0) / (f32(1.0) - f32(np.power(f32(b1), f32(step)))))
-    c2 = np.float64(f32(1.0) / (f32(1.0) - f32(np.power(f32(b2), f32(step)))))
-    mh, vh = r(m * c1), r(v * c2)
-    p = r(p - r(r(lr * mh) / r(r(np.sqrt(vh)) + eps)))
-    return p, m, v
 
 
 def test_adamw_steps_match_reference_formula(pkg):
@@ -57,7 +43,7 @@ def test_adamw_steps_match_reference_formula(pkg):
     for step in (1, 2, 3):
         assert L.adamw_sm100_step(table("p"), table("g"), table("m"), table("v"), lens, n, lr, b1, b2, wd, eps, step, stream) == 0
         for i in range(n):
-            ref["p"][i], ref["m"][i], ref["v"][i] = ref_step(ref["p"][i], ref["g"][i], ref["m"][i], ref["v"][i],
+            ref["p"][i], ref["m"][i], ref["v"][i] = ops.adamw_step(ref["p"][i], ref["g"][i], ref["m"][i], ref["v"][i],
                                                              lr, b1, b2, wd, eps, step)
         for i in range(n):
             for k in ("p", "m", "v"):

@@ -169,6 +169,41 @@ def test_forward_is_deterministic_and_stays_inside_its_buffers(pkg, gpu):
     assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
 
 
+@pytest.mark.parametrize("B,T,H", [(2, 200, 2), (1, 130, 3), (3, 384, 2), (2, 1, 2), (1, 777, 1)])
+def test_forward_and_backward_stay_inside_every_buffer(pkg, gpu, B, T, H):
+    """Every buffer the two calls write (out, out_copy, lse, saved, dqkv, scratch) sits between two padding
+    zones filled with a sentinel; ragged T makes the last tile of every kernel a partial one (stores guarded
+    by t < T, rows past the end dropped by the copy engine).  The zones must come back untouched, and so
+    must the read-only inputs."""
+    torch = gpu
+    D, pad = 64, 8192
+    x, g = seeded(40 + T, B, T, H, D)
+    xt, gt = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    sizes = {"out": B * T * H * D * 4, "out_copy": B * T * H * D * 4, "lse": B * H * T * 4,
+             "saved": pkg.saved_bytes(B, T, H, D), "dqkv": B * T * 3 * H * D * 4,
+             "scratch": pkg.backward_scratch_bytes(B, T, H, D)}
+    raw, view = {}, {}
+    for k, n in sizes.items():
+        n16 = (n + 15) // 16 * 16  # keep the next zone 16-byte aligned
+        raw[k] = torch.full((2 * pad + n16,), 0xA5, device="cuda", dtype=torch.uint8)
+        view[k] = raw[k][pad:pad + n]
+    f32 = lambda k, *shape: view[k].view(torch.float32).view(*shape)  # noqa: E731
+    out, out_copy, lse = f32("out", B, T, H * D), f32("out_copy", B, T, H * D), f32("lse", B, H, T)
+    dqkv = f32("dqkv", B, T, 3 * H * D)
+    pkg.forward_into(xt, out, out_copy, lse, view["saved"], H)
+    pkg.backward_into(view["saved"], out_copy, lse, gt, dqkv, view["scratch"], H)
+    assert pkg.device_status() == 0
+    for k, n in sizes.items():
+        assert bool((raw[k][:pad] == 0xA5).all()), f"{k}: bytes before the buffer were written"
+        assert bool((raw[k][pad + n:] == 0xA5).all()), f"{k}: bytes after the buffer were written"
+    assert torch.equal(xt.cpu(), torch.from_numpy(x)) and torch.equal(gt.cpu(), torch.from_numpy(g))
+    # and the results are the usual ones
+    o2, c2 = pkg.forward(xt, H)
+    d2 = pkg.backward(c2, gt)
+    assert torch.equal(out, o2) and torch.equal(out_copy, o2) and torch.equal(lse, c2.lse)
+    assert float((dqkv - d2).abs().max()) <= 1e-4
+
+
 def test_causality_on_gpu(pkg, gpu):
     x, _ = seeded(35, 1, 300, 2, 64)
     o0, _, _ = run_cuda(pkg, gpu, x, None, 2)

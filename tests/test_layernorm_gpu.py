@@ -1,5 +1,6 @@
-"""Parity of the LayerNorm kernels (include/layernorm_sm100.h) against a float64 numpy restatement of
-the reference's CPU LayerNorm (kernels/src/cpu/LayerNorm.c:5-59 forward, :61-123 backward): mean and
+"""Parity of the LayerNorm kernels (include/layernorm_sm100.h) against the float64 numpy restatement of
+the reference's CPU LayerNorm (kernels/src/cpu/LayerNorm.c:5-59 forward, :61-123 backward) in
+oracle/ops_oracle.py, which tests/test_ops_oracle.py pins to the reference's own kernel: mean and
 E[x^2] in one pass, rstd = 1/sqrt(var + eps); dW += sum dy*xhat, db += sum dy, dx += a*dy*w + b*x + c.
 
 Tolerance: everything is fp32 with fp32 accumulation over C (rows) or over the rows (dW, db), so the
@@ -10,36 +11,11 @@ import numpy as np
 import pytest
 
 torch = pytest.importorskip("torch")
+from oracle import ops_oracle as ops  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(8 * 128, 768), (1000, 768), (333, 1024), (64, 1600), (17, 64), (256, 2048), (5, 4)]
-
-
-def ref_forward(x, w, b, eps):
-    x = x.astype(np.float64)
-    m = x.mean(axis=1, keepdims=True)
-    var = (x * x).mean(axis=1, keepdims=True) - m * m
-    r = 1.0 / np.sqrt(var + eps)
-    y = (x - m) * r * w
-    if b is not None:
-        y = y + b
-    return y, m[:, 0], r[:, 0]
-
-
-def ref_backward(dy, x, mean, rstd, w):
-    dy, x, w = dy.astype(np.float64), x.astype(np.float64), w.astype(np.float64)
-    a = rstd[:, None].astype(np.float64)
-    mu = mean[:, None].astype(np.float64)
-    C = x.shape[1]
-    dw = (dy * (a * x - a * mu)).sum(axis=0)
-    db = dy.sum(axis=0)
-    ds = (dy * x * w).sum(axis=1, keepdims=True)
-    dbs = (dy * w).sum(axis=1, keepdims=True)
-    bb = (dbs * mu - ds) * a ** 3 / C
-    cc = -bb * mu - dbs * a / C
-    dx = a * dy * w + bb * x + cc
-    return dw, db, dx
 
 
 @pytest.mark.parametrize("rows,C", SHAPES)
@@ -55,7 +31,7 @@ def test_layernorm_forward_and_backward_vs_cpu(pkg, rows, C, with_bias):
     bt = torch.from_numpy(b).cuda() if with_bias else None
 
     y, mean, rstd = pkg.layernorm_forward(xt, wt, bt, eps)
-    y_ref, m_ref, r_ref = ref_forward(x, w, b, eps)
+    y_ref, m_ref, r_ref = ops.layernorm_forward(x, w, b, eps)
     assert np.abs(y.cpu().numpy() - y_ref).max() <= 2e-5 * max(1.0, np.abs(y_ref).max())
     assert np.abs(mean.cpu().numpy() - m_ref).max() <= 1e-5
     assert np.abs(rstd.cpu().numpy() / r_ref - 1.0).max() <= 1e-5
@@ -66,7 +42,7 @@ def test_layernorm_forward_and_backward_vs_cpu(pkg, rows, C, with_bias):
     dx0 = rng.standard_normal((rows, C)).astype(np.float32)
     dw, db, dx = (torch.from_numpy(a.copy()).cuda() for a in (dw0, db0, dx0))
     pkg.layernorm_backward(dyt, xt, mean, rstd, wt, dw, db if with_bias else None, dx)
-    dw_ref, db_ref, dx_ref = ref_backward(dy, x, mean.cpu().numpy(), rstd.cpu().numpy(), w)
+    dw_ref, db_ref, dx_ref = ops.layernorm_backward(dy, x, mean.cpu().numpy(), rstd.cpu().numpy(), w)
     scale_cols = max(1.0, np.abs(dw_ref).max(), np.abs(db_ref).max())
     assert np.abs(dw.cpu().numpy() - (dw0 + dw_ref)).max() <= 1e-4 * scale_cols
     if with_bias:

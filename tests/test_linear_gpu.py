@@ -1,6 +1,7 @@
-"""Parity of the tcgen05 Linear kernels (include/linear_sm100.h) against a CPU restatement of the
-reference's Linear (kernels/src/cpu/Linear.c:4-31 forward, :33-88 backward): y = x W^T + b,
-dx = dy W, dW += dy^T x, db += colsum(dy), computed here in float64 with numpy.
+"""Parity of the tcgen05 Linear kernels (include/linear_sm100.h) against the float64 numpy restatement of the
+reference's Linear (kernels/src/cpu/Linear.c:4-31 forward, :33-88 backward) in oracle/ops_oracle.py, pinned to
+the reference's own CPU kernel by tests/test_ops_oracle.py: y = x W^T + b, dx = dy W, dW += dy^T x,
+db += colsum(dy).
 
 Tolerance: the kernels use TF32 inputs (the upper 19 bits of each fp32 operand: truncation, relative
 error below 2^-10 per operand) with fp32 accumulation, the precision class of the reference's CUDA
@@ -12,6 +13,7 @@ import numpy as np
 import pytest
 
 torch = pytest.importorskip("torch")
+from oracle import ops_oracle as ops  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -51,7 +53,7 @@ def inputs(M, N, K, seed):
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_linear_forward_vs_cpu(pkg, M, N, K):
     x, w, b, _ = inputs(M, N, K, 11)
-    ref = x.astype(np.float64) @ w.astype(np.float64).T + b
+    ref = ops.linear_forward(x, w, b)
     y = pkg.linear_forward(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda())
     assert pkg.device_status() == 0
     within(y.cpu().numpy(), ref, x, w.T)
@@ -94,9 +96,7 @@ def test_linear_backward_vs_cpu(pkg, M, N, K):
     rng = np.random.default_rng(99)
     dw0 = rng.standard_normal((N, K), dtype=np.float32)
     db0 = rng.standard_normal(N, dtype=np.float32)
-    dx_ref = dy.astype(np.float64) @ w.astype(np.float64)
-    dw_ref = dw0 + dy.astype(np.float64).T @ x.astype(np.float64)
-    db_ref = db0 + dy.astype(np.float64).sum(axis=0)
+    dx_ref, dw_ref, db_ref = ops.linear_backward(dy, x, w, dw0, db0)
     dw = torch.from_numpy(dw0.copy()).cuda()
     db = torch.from_numpy(db0.copy()).cuda()
     dx = pkg.linear_backward(torch.from_numpy(dy).cuda(), torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), dw, db)
