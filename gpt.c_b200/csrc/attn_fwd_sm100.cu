@@ -68,36 +68,6 @@ enum Site : int {
     SITE_O_FULL_LAST, SITE_PAIR, SITE_Q_TMEM, SITE_EPI_BAR
 };
 
-// Optional cycle trace of CTA 0 (debug builds with -DATTN_TRACE only).
-#ifdef ATTN_TRACE
-__device__ long long g_fwd_trace[3 * 16 * 8];
-#define FWD_TRACE(cond, role, tile, k)                                                              \
-    do {                                                                                            \
-        if (blockIdx.x == 0 && (cond)) g_fwd_trace[((role) * 16 + (tile)) * 8 + (k)] = clock64();  \
-    } while (0)
-// life time of every 48th CTA in ns: slot 2, [cta / 48][0..2] = start, set-up done, end
-#define FWD_LIFE(k)                                                                                         \
-    do {                                                                                                    \
-        if (threadIdx.x == 0 && blockIdx.x % 48 == 0)                                                       \
-            g_fwd_trace[(2 * 16 + blockIdx.x / 48) * 8 + (k)] = (long long)global_timer_ns();               \
-    } while (0)
-// phases of one light CTA (the last one) in ns: slot 1, row 15
-#define FWD_PHASE(cond, k)                                                                        \
-    do {                                                                                          \
-        if (blockIdx.x == gridDim.x - 1 && (cond)) g_fwd_trace[(1 * 16 + 15) * 8 + (k)] = (long long)global_timer_ns(); \
-    } while (0)
-#else
-#define FWD_PHASE(cond, k) \
-    do {                   \
-    } while (0)
-#define FWD_LIFE(k) \
-    do {            \
-    } while (0)
-#define FWD_TRACE(cond, role, tile, k) \
-    do {                               \
-    } while (0)
-#endif
-
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -190,8 +160,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     WaitCtx ctx{&sm.abort_flag, status};
     pdl_launch_dependents();
-    FWD_LIFE(0);
-    FWD_PHASE(threadIdx.x == 128, 0);
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
@@ -236,7 +204,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
-    FWD_LIFE(1);
 
     if (warp == 0) {
         // ------------------------------ TMA producer: K ------------------------------
@@ -277,7 +244,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int st = j & 1;
             if (!mbar_wait_warp(&sm.k_full[st], (j >> 1) & 1, ctx, SITE_K_FULL)) return false;
             tc_fence_after_sync();
-            FWD_TRACE(lane == 0, 0, j & 15, 1);
             const uint64_t kd[2] = {smem_desc_sw128(smem_u32(sm.k[st][0]), 16, 1024),
                                     smem_desc_sw128(smem_u32(sm.k[st][1]), 16, 1024)};
             uint32_t acc = 0;
@@ -293,7 +259,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             tc_commit_lead(leader, &sm.s_full[st]);
             tc_commit_lead(leader, &sm.k_empty[st]);
-            FWD_TRACE(lane == 0, 0, j & 15, 2);
             return true;
         };
         if (ok) ok = issue_qk(0);
@@ -304,7 +269,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (!mbar_wait_warp(&sm.v_full[st], (j >> 1) & 1, ctx, SITE_V_FULL)) break;
             if (!mbar_wait_warp(&sm.p_full[st], (j >> 1) & 1, ctx, SITE_P_FULL)) break;
             tc_fence_after_sync();
-            FWD_TRACE(lane == 0, 0, j & 15, 3);
             const uint64_t vd[2] = {smem_desc_sw128(smem_u32(sm.v[st][0]), 1024, 1024),
                                     smem_desc_sw128(smem_u32(sm.v[st][1]), 1024, 1024)};
             uint32_t acc = j >= 1 ? 1u : 0u;
@@ -320,7 +284,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             tc_commit_lead(leader, &sm.o_full);
             tc_commit_lead(leader, &sm.v_empty[st]);
-            FWD_TRACE(lane == 0, 0, j & 15, 4);
         }
     } else if (warp >= 4) {
         // ------------------------------ softmax ------------------------------
@@ -336,7 +299,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // copy this thread's Q row (half 0: hi plane, half 1: lo plane) from the swizzled shared
         // memory tile into tensor memory: 64 bf16 = 32 packed columns, lane = row
         if (mbar_wait_warp(&sm.q_full, 0, ctx, SITE_Q_FULL)) {
-            FWD_PHASE(threadIdx.x == 128, 1);
             const uint8_t *qrow = sm.q[half] + row * 128;
             uint32_t r[32];
 #pragma unroll
@@ -351,7 +313,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.q_tmem);
-            FWD_PHASE(threadIdx.x == 128, 2);
         }
         bool ok = true;
 
@@ -360,17 +321,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const uint32_t t_s = tmem + lane_addr + kColS + st * kStep;
             const int key0 = j * kStep - qt * kTile;  // first key of the step relative to the tile's first row
             const bool diag = key0 + kStep - 1 > 0;   // some (row, key) pair of this step is above the diagonal
-            FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 0);
             if (!mbar_wait_warp(&sm.s_full[st], par, ctx, SITE_S_FULL)) { ok = false; break; }
             tc_fence_after_sync();
-            FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 1);
-            if (j == 0) FWD_PHASE(threadIdx.x == 128, 3);
             float alpha;
             const bool step_ok = diag
                 ? max_pass<true>(sm, ctx, t_s, row, half, j & 1, key0, pair_bar, scale_log2, m, alpha)
                 : max_pass<false>(sm, ctx, t_s, row, half, j & 1, key0, pair_bar, scale_log2, m, alpha);
             if (!step_ok) { ok = false; break; }
-            FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 2);
             // When the reference maximum of some row of this warp moved, rescale the warp's 32 rows x
             // 32 columns of O in place: after the previous PV product has finished, before P_j is
             // published.
@@ -386,12 +343,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             l = l * alpha + (diag ? exp_pass<true>(t_s, row, half, key0, scale_log2, m)
                                   : exp_pass<false>(t_s, row, half, key0, scale_log2, m));
-            FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 5);
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.p_full[st]);
-            FWD_TRACE(lane == 0 && half == 0 && quarter == 0, 1, j & 15, 6);
-            if (j == nsteps - 1) FWD_PHASE(threadIdx.x == 128, 4);
         }
 
         // epilogue: O / l for this thread's 32 columns, log-sum-exp by the first half
@@ -399,7 +353,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ok && mbar_wait_warp(&sm.o_full, (nsteps - 1) & 1, ctx, SITE_O_FULL_LAST)) {
             tc_fence_after_sync();
-            FWD_PHASE(threadIdx.x == 128, 5);
             uint32_t r[32];
             tmem_ld32(t_o, r);
             tmem_wait_ld();
@@ -453,17 +406,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);
     }
-    FWD_LIFE(2);
-    FWD_PHASE(threadIdx.x == 128, 6);
 }
 
 }  // namespace
-
-#ifdef ATTN_TRACE
-extern "C" int attn_fwd_trace_read(long long *dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_fwd_trace, sizeof(g_fwd_trace));
-}
-#endif
 
 static size_t fwd_smem_bytes() { return sizeof(FwdSmem) + 1024; }
 
