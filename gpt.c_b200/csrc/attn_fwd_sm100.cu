@@ -55,6 +55,7 @@ struct __align__(1024) FwdSmem {
     uint8_t v[2][2][kPlaneStep];
     uint64_t q_full, q_tmem, k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t s_full[2], p_full[2], o_full;
+    uint64_t o_done;            // the last PV product has completed
     uint64_t epi_bar;           // every softmax thread has staged its part of the output tile
     uint64_t pair_bar[4];       // [quarter]: the two halves of a row block meet here once per tile
     float xmax[2][2][kTile];    // [tile parity][half][row]: row maxima exchanged between halves
@@ -174,6 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             mbar_init(&sm.p_full[i], kSoftmaxThreads);
         }
         mbar_init(&sm.o_full, 1);
+        mbar_init(&sm.o_done, 1);
         mbar_init(&sm.epi_bar, kSoftmaxThreads);
         for (int i = 0; i < 4; i++) mbar_init(&sm.pair_bar[i], 64);
         fence_barrier_init();
@@ -284,6 +286,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             tc_commit_lead(leader, &sm.o_full);
             tc_commit_lead(leader, &sm.v_empty[st]);
+            if (j == nsteps - 1) tc_commit_lead(leader, &sm.o_done);
         }
     } else if (warp >= 4) {
         // ------------------------------ softmax ------------------------------
@@ -351,7 +354,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // epilogue: O / l for this thread's 32 columns, log-sum-exp by the first half
         sm.lpart[half][row] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ok && mbar_wait_warp(&sm.o_full, (nsteps - 1) & 1, ctx, SITE_O_FULL_LAST)) {
+        // The last product has a barrier of its own: o_full completes once per key step and this thread has
+        // not followed its phases, so a parity wait on it could not tell the last product from the one before
+        // (with two key steps the first PV can still be running here).
+        if (ok && mbar_wait_warp(&sm.o_done, 0, ctx, SITE_O_FULL_LAST)) {
             tc_fence_after_sync();
             uint32_t r[32];
             tmem_ld32(t_o, r);
