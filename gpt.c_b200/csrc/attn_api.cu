@@ -173,7 +173,8 @@ size_t attn_sm100_saved_bytes(int B, int T, int H, int D) {
 
 size_t attn_sm100_backward_scratch_bytes(int B, int T, int H, int D) {
     if (!shape_ok(B, T, H, D)) return 0;
-    return 2 * attn::plane_bytes((size_t)B * T * H * D) + attn::align_up((size_t)B * H * T * sizeof(float), 256);
+    // dO planes, delta, and the two ints of the backward kernel's item counter
+    return 2 * attn::plane_bytes((size_t)B * T * H * D) + attn::align_up((size_t)B * H * T * sizeof(float), 256) + 256;
 }
 
 int attn_sm100_forward(const float *qkv, float *out, float *out_copy, float *lse, void *saved, int B, int T, int H,
@@ -239,12 +240,14 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
     __nv_bfloat16 *dhi = static_cast<__nv_bfloat16 *>(scratch);
     __nv_bfloat16 *dlo = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(scratch) + oplane);
     float *delta = reinterpret_cast<float *>(static_cast<char *>(scratch) + 2 * oplane);
+    int *sched = reinterpret_cast<int *>(static_cast<char *>(scratch) + 2 * oplane +
+                                         attn::align_up((size_t)B * H * T * sizeof(float), 256));
 
     cudaError_t e = cudaSuccess;
     const bool prepare = !(flags & ATTN_FLAG_CORE_ONLY), core = !(flags & ATTN_FLAG_PREPARE_ONLY);
     if (fast) {
         if (prepare) {
-            e = attn::launch_bwd_prepare(dout, out, delta, dhi, dlo, dqkv, B, T, H, D, s);
+            e = attn::launch_bwd_prepare(dout, out, delta, dhi, dlo, dqkv, sched, B, T, H, D, s);
             if (e != cudaSuccess) return (int)e;
         }
         if (!core) return ATTN_OK;
@@ -255,10 +258,10 @@ int attn_sm100_backward(const void *saved, const float *out, const float *lse, c
         if (rc != 0) return rc;
         rc = encode_rows_f32(&map_dx, dqkv, B, T, 3 * H * D);
         if (rc != 0) return rc;
-        e = attn::launch_fast_backward(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, ds->num_sms, ds->status, s);
+        e = attn::launch_fast_backward(map_x, map_do, map_dx, lse, delta, dqkv, B, T, H, ds->num_sms, sched, ds->status, s);
     } else {
         if (prepare) {
-            e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, B, T, H, D, s);
+            e = attn::launch_bwd_prepare(dout, out, delta, nullptr, nullptr, nullptr, nullptr, B, T, H, D, s);
             if (e != cudaSuccess) return (int)e;
         }
         if (!core) return ATTN_OK;

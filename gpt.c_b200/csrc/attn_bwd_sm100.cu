@@ -5,14 +5,16 @@
 // permute-accumulate become one kernel that recomputes the probabilities from the saved
 // log-sum-exp and never writes a T x T matrix.
 //
-// The kernel is persistent: one CTA per SM walks a list of work items.  A work item is one (batch,
+// The kernel is persistent: one CTA per SM takes work items from a list.  A work item is one (batch,
 // head) and one tile of 128 keys (K_j, V_j stay in shared memory) together with the query tiles
-// i = j .. last.  Items are ordered heaviest first (key tile 0 sees every query tile) and dealt to
-// the CTAs in a snake (round r goes left to right when r is even, right to left when it is odd),
-// which balances the SMs as well as a greedy longest-first assignment does without any counter in
-// global memory.  Barriers, tensor memory and the Q/dO ring live for the whole launch; the K/V
-// tiles of the next item are requested as soon as the last tensor-core instruction that reads the
-// current ones has completed, so that set-up of item w+1 overlaps the drain of item w.
+// i = j .. last.  Items are ordered heaviest first (key tile 0 sees every query tile); a CTA starts
+// with the item of its own number and takes every further one from a counter in global memory, one
+// item ahead of the one it works on, so an SM that runs slower than the others (the time of the same
+// work differs by +-7 % between SMs) simply takes fewer of the small items at the end.  A fixed deal
+// of the items left the slowest CTA 9 % behind the average.  Barriers, tensor memory and the Q/dO
+// ring live for the whole launch; the K/V tiles of the next item are requested as soon as the last
+// tensor-core instruction that reads the current ones has completed, so that set-up of item w+1
+// overlaps the drain of item w.
 //
 // Everything is computed transposed so that the key index is the tensor-memory lane:
 //     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (B = Q / dO half, K-major)
@@ -80,6 +82,8 @@ constexpr int kThreads = 640;
 constexpr int kGradWarp = 3;
 constexpr int kComputeThreads = 512;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kQueue = 4;  // a slot is rewritten when every role has long read it
+constexpr int kMoreBit = 1 << 30;
 constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 320, kColDQ = 384, kColKH = 448, kColVH = 480;
 
 struct __align__(1024) BwdSmem {
@@ -109,6 +113,12 @@ struct __align__(1024) BwdSmem {
     uint64_t ds_full;                  // dS^T of both halves is in shared memory
     uint64_t dq_full[2];               // [tile parity]
     uint64_t stats_full[2], stats_free[2];  // [statistics buffer]
+    // The CTA's items in the order it takes them (ItemFeed).  q_raw[k % kQueue]: number of item k, or a
+    // number past the end of the list; q_item[k % kQueue]: the same with kMoreBit set when item k + 1
+    // exists, posted only for items that exist, one completion of q_full per post.
+    uint64_t q_full[kQueue];
+    int q_item[kQueue];
+    int q_raw[kQueue];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -116,30 +126,36 @@ struct __align__(1024) BwdSmem {
 enum Site : int {
     SITE_IN_EMPTY = 101, SITE_IN_FULL, SITE_KV_FULL, SITE_ST_FULL, SITE_DQ_FULL_FREE, SITE_DQ_FULL_LAST, SITE_ROW_BAR,
     SITE_PDS_FULL, SITE_STATS_FREE, SITE_KV_TMEM, SITE_DS_FULL, SITE_GRADS_DONE, SITE_SMEM_ALIGN, SITE_V_FREE, SITE_K_FREE,
-    SITE_KV_OUT_FULL, SITE_STAGE_FREE, SITE_TMEM_BASE, SITE_OUT_FULL, SITE_OUT_FREE
+    SITE_KV_OUT_FULL, SITE_STAGE_FREE, SITE_TMEM_BASE, SITE_OUT_FULL, SITE_OUT_FREE, SITE_QUEUE
 };
 
-// Work list of one CTA.  Item p (0 = heaviest) is key tile p / BH of (batch, head) p % BH; round r of
-// the deal gives CTA c item r * G + c when r is even and r * G + (G - 1 - c) when it is odd.  Every
-// role of the CTA walks the same list with its own copy of this iterator.
+// Item p of the list (0 = heaviest) is key tile p / BH of (batch, head) p % BH.
 struct Work {
     int jt, bh, niter;
 };
-struct WorkList {
-    int grid, cta, nitems, BH, nt, round;
-    __device__ WorkList(int BH_, int nt_) : grid((int)gridDim.x), cta((int)blockIdx.x), nitems(BH_ * nt_), BH(BH_), nt(nt_), round(0) {}
-    __device__ bool next(Work &w) {
-        while (round * grid < nitems) {
-            const int r = round++;
-            const int p = r * grid + ((r & 1) ? grid - 1 - cta : cta);
-            if (p < nitems) {
-                w.jt = p / BH;
-                w.bh = p - w.jt * BH;
-                w.niter = nt - w.jt;  // query tiles jt .. nt-1
-                return true;
-            }
-        }
-        return false;
+__device__ __forceinline__ Work decode_item(int p, int BH, int nt) {
+    Work w;
+    w.jt = p / BH;
+    w.bh = p - w.jt * BH;
+    w.niter = nt - w.jt;  // query tiles jt .. nt-1
+    return w;
+}
+
+// How a role learns the CTA's items.  Item 0 is the CTA's own number and item 1 its mirror image in the
+// second round (as in a snake deal), so the first entry needs no communication; entry k >= 1 is read from
+// BwdSmem::q_item with a plain load once the role has passed the first barrier wait of item k that it
+// performs anyway (the entry was posted more than an item earlier, and the poster has completed barriers
+// the role has waited for since).  Keeping a barrier wait with its time-out out of the roles' item loops
+// matters: with one in, the compiler's code for the compute warps ran 7 % slower.
+struct ItemFeed {
+    int p;      // number of the current item
+    bool more;  // another item follows
+    __device__ ItemFeed(int nitems) : p((int)blockIdx.x), more(2 * (int)gridDim.x - 1 - (int)blockIdx.x < nitems) {}
+    // entry k (k >= 1); the caller has made sure it has been posted
+    __device__ __forceinline__ void read(const BwdSmem &sm, uint32_t k) {
+        const int e = *reinterpret_cast<const volatile int *>(&sm.q_item[k % kQueue]);
+        p = e & (kMoreBit - 1);
+        more = (e & kMoreBit) != 0;
     }
 };
 
@@ -197,7 +213,7 @@ __device__ __forceinline__ void store_ds(uint8_t *tile_h, uint8_t *tile_l, int r
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_dx, const float *__restrict__ lse, const float *__restrict__ delta,
-                float *__restrict__ dqkv, int B, int T, int H, float scale, float scale_log2, int *status) {
+                float *__restrict__ dqkv, int B, int T, int H, float scale, float scale_log2, int *sched, int *status) {
     // The structure fills the whole 227 KiB, so there is no room to round the base up: the
     // swizzled tiles need 1024-byte alignment and the kernel refuses to run without it.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -238,6 +254,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             mbar_init(&sm.in_empty[i], 1);
         }
         mbar_init(&sm.ds_full, kComputeThreads);
+        for (int i = 0; i < kQueue; i++) mbar_init(&sm.q_full[i], 1);
         fence_barrier_init();
     }
     if (warp == 2) {
@@ -254,7 +271,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // instruction that takes it); an allocation anywhere else is reported and the CTA does nothing.
     constexpr uint32_t tmem = 0;
     const bool tmem_ok = sm.tmem_base == tmem;
-    WorkList work(BH, nt);
+    ItemFeed feed(BH * nt);
     Work w;
 
     if (!tmem_ok) {
@@ -290,16 +307,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         tma_load_4d(dst[pl] + hf * kPlaneHalf, &map_x, &sm.kv_full, x0, it.jt * kTile + hf * kHalf, b, pl);
             };
             Work nxt;
-            bool has = work.next(w);
-            if (has) {
-                mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
-                load_kv(w, sm.k, C + (w.bh % H) * kD);
-                load_kv(w, sm.v, 2 * C + (w.bh % H) * kD);
-            }
+            bool has = true;
+            w = decode_item(feed.p, BH, nt);
+            mbar_expect_tx(&sm.kv_full, 4 * kPlaneTile);
+            load_kv(w, sm.k, C + (w.bh % H) * kD);
+            load_kv(w, sm.v, 2 * C + (w.bh % H) * kD);
             int pre = 0;  // half tiles of the current item already requested
             for (uint32_t item = 0; has && ok; item++) {
                 for (int t = pre; ok && t < 2 * w.niter; t++) load_half(w, t);
-                const bool has_next = work.next(nxt);
+                // the next item: its entry is the (item + 1)-th post, made while the CTA worked on the item
+                // before this one
+                const bool has_next = feed.more;
+                if (has_next) {
+                    if (!mbar_wait(&sm.q_full[(item + 1) % kQueue], ((item + 1) / kQueue) & 1, ctx, SITE_QUEUE)) break;
+                    feed.read(sm, item + 1);
+                    nxt = decode_item(feed.p, BH, nt);
+                }
                 pre = 0;
                 if (has_next && ok) {
                     // The next item's tiles, each as soon as its destination is free: the first Q/dO half
@@ -337,8 +360,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // those (gradient task g-2, issued by another warp) must have completed.
         uint32_t g = 0;
         bool ok = true;
-        for (uint32_t item = 0; ok && work.next(w); item++) {
+        for (uint32_t item = 0; ok; item++) {
             ok = mbar_wait_warp(&sm.kv_tmem, item & 1, ctx, SITE_KV_TMEM);
+            if (!ok) break;
+            if (item > 0) feed.read(sm, item);
+            w = decode_item(feed.p, BH, nt);
             for (int t = 0; ok && t < 2 * w.niter; t++, g++) {
                 const int hf = t & 1;
                 const uint32_t slot = g % kSlots;
@@ -381,6 +407,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 tc_commit_lead(leader, &sm.st_full[hf]);
                 if (t == 2 * w.niter - 1) tc_commit_lead(leader, &sm.v_free);
             }
+            if (!feed.more) break;
         }
     } else if (warp == 2) {
         // ------------------------------ row statistics and output copies ------------------------------
@@ -392,20 +419,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // tile), the dK / dV tiles of a finished item are plain stores; rows past the end of the sequence
         // are dropped by the copy engine.
         if (lane == 0) tma_prefetch_desc(&map_dx);
-        struct TileCursor {  // the query tiles of this CTA's items, in processing order
-            WorkList wl;
+        // The query tiles of this CTA's items, in processing order.  This warp hands the items out (below)
+        // and reads their numbers from q_raw, which it has written itself.
+        const int nitems = BH * nt, G = (int)gridDim.x;
+        struct TileCursor {
             Work w;
             int m;
-            bool valid;
-            __device__ TileCursor(int BH_, int nt_) : wl(BH_, nt_), m(0) { valid = wl.next(w); }
+            uint32_t item;
+            bool valid, pending;
+            __device__ TileCursor() : m(0), item(0), valid(true), pending(true) {}
+            __device__ bool ready(const BwdSmem &sm, int BH, int nt) {  // all lanes, after a __syncwarp behind q_raw's writer
+                if (pending) {
+                    const int p = *reinterpret_cast<const volatile int *>(&sm.q_raw[item % kQueue]);
+                    valid = p < BH * nt;
+                    if (valid) w = decode_item(p, BH, nt);
+                    pending = false;
+                }
+                return valid;
+            }
             __device__ void advance() {
                 if (++m >= w.niter) {
                     m = 0;
-                    valid = wl.next(w);
+                    item++;
+                    pending = true;
                 }
             }
         };
-        TileCursor cur(BH, nt), ahead(BH, nt);
+        TileCursor cur, ahead;
         auto stage_stats = [&](const TileCursor &c, uint32_t n) {
             const int buf = n & 1;
 #pragma unroll
@@ -416,9 +456,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             mbar_arrive(&sm.stats_full[buf]);
         };
-        for (uint32_t n = 0; n < 2 && ahead.valid; n++) {
-            stage_stats(ahead, n);
-            ahead.advance();
+        // Handing out the items.  The first two are fixed (ItemFeed); every further one comes from the
+        // counter in global memory.  The number of item k + 3 is asked for when this warp begins the last query
+        // tile of item k and used at the end of that tile's round, when the answer (a microsecond or two) has
+        // long arrived: it goes to q_raw for this warp's own look-ahead of two query tiles, which therefore
+        // never waits for a number, and it completes the entry of item k + 2, which tells the other roles
+        // whether an item k + 3 follows.  The small items at the end of the list are thus still handed out
+        // two or three at a time.  (The producer warp is the wrong place to ask: the request held up its
+        // tile requests by over a thousand cycles.)
+        auto ask = [&](int last_known) -> uint32_t {  // lane 0 holds the answer
+            uint32_t ticket = 0;
+            if (last_known < nitems && lane == 0)
+                asm volatile("atom.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(sched) : "memory");
+            return ticket;
+        };
+        auto answer = [&](int last_known, uint32_t ticket) -> int {
+            return last_known < nitems ? 2 * G + (int)__shfl_sync(0xffffffffu, ticket, 0) : nitems;
+        };
+        // item `k` gets its number `p` in q_raw; the entry of item k - 1 (number `p_before`) is complete with it
+        auto hand_out = [&](uint32_t k, int p, int p_before) {
+            if (lane == 0) {
+                sm.q_raw[k % kQueue] = p;
+                if (p_before < nitems) {
+                    sm.q_item[(k - 1) % kQueue] = p_before | (p < nitems ? kMoreBit : 0);
+                    mbar_arrive(&sm.q_full[(k - 1) % kQueue]);  // releases the store above
+                }
+            }
+            __syncwarp();
+        };
+        int p_last = 2 * G - 1 - (int)blockIdx.x;  // number of the last item known (item 1)
+        uint32_t known = 2;  // items whose numbers are known
+        if (lane == 0) {
+            sm.q_raw[0] = (int)blockIdx.x;
+            sm.q_raw[1] = p_last;
+            if (nitems > 0) {
+                sm.q_item[0] = (int)blockIdx.x | (p_last < nitems ? kMoreBit : 0);
+                mbar_arrive(&sm.q_full[0]);
+            }
+        }
+        __syncwarp();
+        {
+            const uint32_t ticket = ask(p_last);
+            for (uint32_t n = 0; n < 2 && ahead.ready(sm, BH, nt); n++) {
+                stage_stats(ahead, n);
+                ahead.advance();
+            }
+            const int p = answer(p_last, ticket);
+            hand_out(known++, p, p_last);
+            p_last = p;
         }
         // the staged dQ tile of query tile `qt` -> dq third of dqkv
         auto reduce_dq = [&](const Work &it, int qt) {
@@ -434,12 +519,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         };
         bool ok = true;
         uint32_t item = 0;  // items finished
-        for (uint32_t n = 0; ok && cur.valid; n++) {
+        for (uint32_t n = 0; ok && cur.ready(sm, BH, nt); n++) {
+            const bool last_tile = cur.m == cur.w.niter - 1;
+            uint32_t ticket = 0;
+            if (last_tile) ticket = ask(p_last);
             if (cur.m >= 1) {  // dQ of the item's previous query tile (staged after half A of this one)
                 if (!mbar_wait_warp(&sm.out_full, (n - 1) & 1, ctx, SITE_OUT_FULL)) break;
                 reduce_dq(cur.w, cur.w.jt + cur.m - 1);
             }
-            if (ahead.valid) {  // statistics two tiles ahead, into the buffer tile n releases
+            if (ahead.ready(sm, BH, nt)) {  // statistics two tiles ahead, into the buffer tile n releases
                 if (!mbar_wait_warp(&sm.stats_free[n & 1], (n >> 1) & 1, ctx, SITE_STATS_FREE)) break;
                 stage_stats(ahead, n + 2);
                 ahead.advance();
@@ -462,6 +550,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (!mbar_wait_warp(&sm.out_full, n & 1, ctx, SITE_OUT_FULL)) break;
                 reduce_dq(cur.w, cur.w.jt + cur.m);
                 item++;
+            }
+            if (last_tile) {
+                const int p = answer(p_last, ticket);
+                hand_out(known++, p, p_last);
+                p_last = p;
             }
             cur.advance();
         }
@@ -505,12 +598,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             mbar_arrive(&sm.out_full);
         };
 
-        for (uint32_t item = 0; ok && work.next(w); item++) {
+        for (uint32_t item = 0; ok; item++) {
             // K hi and V hi, this thread's 16 head-dim values of key `row`, into tensor memory (packed
             // pairs, so 8 columns each); the rows in shared memory are 128-byte swizzled.  The previous
             // item's last score products, the readers of these columns, completed before this thread left
             // that item's loop.
             if (!mbar_wait_warp(&sm.kv_full, item & 1, ctx, SITE_KV_FULL)) { ok = false; break; }
+            if (item > 0) feed.read(sm, item);
+            w = decode_item(feed.p, BH, nt);
             {
                 uint32_t kh[8], vh[8];
 #pragma unroll
@@ -588,6 +683,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (!mbar_wait_warp(&sm.dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, ctx, SITE_DQ_FULL_LAST)) { ok = false; break; }
             flush_dq();
             tc_fence_before_sync();  // the reads above are ordered before the next item's arrivals
+            if (!feed.more) break;
         }
     } else if (warp == kGradWarp) {
         // ------------------------------ MMA issuer: dV, dK, dQ ------------------------------
@@ -604,7 +700,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const uint32_t leader = elect_leader();
         uint32_t g = 0, n = 0;  // half tiles / query tiles issued so far in this launch
         bool ok = true;
-        while (ok && work.next(w)) {
+        for (uint32_t item = 0; ok; item++) {
+            // the item's entry has been posted and read by the compute warps before they arrive here
+            if (!mbar_wait_warp(&sm.kv_tmem, item & 1, ctx, SITE_KV_TMEM)) break;
+            if (item > 0) feed.read(sm, item);
+            w = decode_item(feed.p, BH, nt);
             for (int m = 0; ok && m < w.niter; m++, n++) {
                 for (int hf = 0; hf < 2; hf++, g++) {
                     if (!mbar_wait_warp(&sm.pds_full[hf], n & 1, ctx, SITE_PDS_FULL)) { ok = false; break; }
@@ -656,6 +756,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 tc_commit_lead(leader, &sm.dq_full[n & 1]);
                 if (m == w.niter - 1) tc_commit_lead(leader, &sm.k_free);
             }
+            if (!feed.more) break;
         }
     }
 
@@ -666,6 +767,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (warp == 2) {
         tc_fence_after_sync();
         tmem_dealloc(sm.tmem_base, kTmemCols);
+    }
+    // the last CTA to finish leaves the item counter as the next launch expects it
+    if (threadIdx.x == 0 && atomicAdd(sched + 1, 1) == (int)gridDim.x - 1) {
+        sched[0] = 0;
+        sched[1] = 0;
     }
 }
 
@@ -680,16 +786,18 @@ cudaError_t fast_bwd_set_attributes() {
 
 // map_x / map_do must have boxes of 64 rows (see the producer warp); map_dx covers dqkv as fp32
 // {3C, T, B} with boxes of 32 columns x 128 rows, 128-byte swizzle.  `num_sms` CTAs at most: one per SM,
-// each walking its share of the (batch, head, key tile) items.
+// each taking (batch, head, key tile) items until none is left.  `sched` points at two ints that are zero
+// when the kernel starts (the item counter and the number of CTAs that have finished) and zero again when
+// it has completed.
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx,
                                  const float *lse, const float *delta, float *dqkv, int B, int T, int H, int num_sms,
-                                 int *status, cudaStream_t s) {
+                                 int *sched, int *status, cudaStream_t s) {
     const int nt = (T + kTile - 1) / kTile;
     const long long items = (long long)nt * B * H;
     const unsigned grid = (unsigned)(items < num_sms ? items : num_sms);
     const float scale = 0.125f;  // 1/sqrt(64)
     return launch_after_previous(attn_bwd_kernel, dim3(grid), dim3(kThreads), bwd_smem_bytes(), s, map_x, map_do, map_dx, lse,
-                                 delta, dqkv, B, T, H, scale, scale * 1.4426950408889634f, status);
+                                 delta, dqkv, B, T, H, scale, scale * 1.4426950408889634f, sched, status);
 }
 
 }  // namespace attn

@@ -113,9 +113,10 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const float *__restric
 __global__ void __launch_bounds__(256) bwd_prepare64_kernel(const float *__restrict__ dout, const float *__restrict__ out,
                                                              float *__restrict__ delta, __nv_bfloat16 *__restrict__ dhi,
                                                              __nv_bfloat16 *__restrict__ dlo, float *__restrict__ dq_zero,
-                                                             int B, int T, int H) {
+                                                             int *__restrict__ sched, int B, int T, int H) {
     tc05::pdl_launch_dependents();
     tc05::pdl_wait();
+    if (sched && blockIdx.x == 0 && threadIdx.x < 2) sched[threadIdx.x] = 0;  // item counter of the backward core
     const int C = H * 64;
     const size_t nvec = (size_t)B * T * C / 8;  // multiple of 8, so whole groups of 8 lanes stay together
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -341,13 +342,13 @@ cudaError_t launch_split(const float *x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, s
 }
 
 cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta, __nv_bfloat16 *dhi,
-                               __nv_bfloat16 *dlo, float *dq_zero, int B, int T, int H, int D, cudaStream_t s) {
+                               __nv_bfloat16 *dlo, float *dq_zero, int *sched, int B, int T, int H, int D, cudaStream_t s) {
     if (D == 64 && dhi && dlo && dq_zero) {
         const size_t nvec = (size_t)B * T * H * 8;
         size_t blocks = (nvec + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
         return launch_after_previous(bwd_prepare64_kernel, dim3((unsigned)blocks), dim3(256), 0, s, dout, out, delta, dhi,
-                                     dlo, dq_zero, B, T, H);
+                                     dlo, dq_zero, sched, B, T, H);
     }
     const size_t rows = (size_t)B * T * H;
     size_t blocks = (rows + 7) / 8;

@@ -22,9 +22,10 @@ inline size_t plane_bytes(size_t n) { return align_up(n * sizeof(__nv_bfloat16),
 cudaError_t launch_split(const float *x, __nv_bfloat16 *hi, __nv_bfloat16 *lo, size_t n, cudaStream_t s);
 
 // rowsum(dout * out) per (b, h, t) -> delta [B, H, T]; also splits dout into bf16 planes when
-// dhi/dlo are given, and zero-fills the dq third of `dq_zero` ([B, T, 3C]) when it is given.
+// dhi/dlo are given, zero-fills the dq third of `dq_zero` ([B, T, 3C]) when it is given, and zeroes the
+// two ints at `sched` (the item counter of the tensor-core backward kernel) when that is given.
 cudaError_t launch_bwd_prepare(const float *dout, const float *out, float *delta, __nv_bfloat16 *dhi,
-                               __nv_bfloat16 *dlo, float *dq_zero, int B, int T, int H, int D, cudaStream_t s);
+                               __nv_bfloat16 *dlo, float *dq_zero, int *sched, int B, int T, int H, int D, cudaStream_t s);
 
 // General-shape SIMT kernels (any D <= kGenericMaxD, T <= kGenericMaxT).
 cudaError_t generic_set_attributes();
@@ -43,7 +44,7 @@ cudaError_t launch_fast_forward(const CUtensorMap &map_x, const CUtensorMap *map
                                 float *out, float *out_copy, float *lse, int B, int T, int H, int *status, cudaStream_t s);
 cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &map_do, const CUtensorMap &map_dx,
                                  const float *lse, const float *delta, float *dqkv, int B, int T, int H, int num_sms,
-                                 int *status, cudaStream_t s);
+                                 int *sched, int *status, cudaStream_t s);
 
 // Launches `kernel` so that it may begin (up to its pdl_wait(), tc05.cuh) while the previous kernel of the
 // stream is still running: its launch latency and set-up overlap that kernel's tail.

@@ -109,22 +109,29 @@ struct WaitCtx {
 #define TC05_WAIT_LIMIT_NS 1000000000ull  // one second
 #endif
 
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.cta_abort) return false;
+// The part of a wait that is only reached when the first probe fails.  Not inlined: the kernels have
+// dozens of waits, and the time-out logic repeated at each of them made their code a tenth larger.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, volatile int *cta_abort, int *status,
+                                            uint64_t limit_ns, int site) {
+    if (*cta_abort) return false;
     const uint64_t t0 = global_timer_ns();
-    const uint64_t limit = ctx.limit_ns ? ctx.limit_ns : TC05_WAIT_LIMIT_NS;
+    const uint64_t limit = limit_ns ? limit_ns : TC05_WAIT_LIMIT_NS;
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++it & 63u) == 0u) {
-            if (*ctx.cta_abort) return false;
+            if (*cta_abort) return false;
             if (global_timer_ns() - t0 > limit) break;
         }
     }
-    *ctx.cta_abort = 1;
-    if (ctx.status) atomicCAS(ctx.status, 0, ST_TIMEOUT_BASE + site);
+    *cta_abort = 1;
+    if (status) atomicCAS(status, 0, ST_TIMEOUT_BASE + site);
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, int site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, ctx.cta_abort, ctx.status, ctx.limit_ns, site);
 }
 
 // Warp-uniform variant for warps that go on to execute .sync.aligned instructions: either every

@@ -90,8 +90,10 @@ int attn_sm100_init(void);
 size_t attn_sm100_saved_bytes(int B, int T, int H, int D);
 
 /*
- * Size in bytes of the scratch buffer backward needs (bf16 hi/lo split of dout and one fp32 per
- * (b, h, t) for rowsum(dout * out)).  Returns 0 for an invalid shape.
+ * Size in bytes of the scratch buffer backward needs (bf16 hi/lo split of dout, one fp32 per
+ * (b, h, t) for rowsum(dout * out), and the counter from which the backward kernel's thread blocks
+ * take their work items; the preparation stage of attn_sm100_backward initialises all of it).
+ * Returns 0 for an invalid shape.
  */
 size_t attn_sm100_backward_scratch_bytes(int B, int T, int H, int D);
 

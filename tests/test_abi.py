@@ -44,7 +44,8 @@ def test_size_queries(pkg):
     # two bf16 planes of B*T*3C elements, each padded to 256 bytes
     assert pkg.saved_bytes(8, 1024, 12, 64) == 2 * 8 * 1024 * 3 * 768 * 2
     assert pkg.saved_bytes(1, 1, 1, 3) == 2 * 256
-    assert pkg.backward_scratch_bytes(8, 1024, 12, 64) == 2 * 8 * 1024 * 768 * 2 + 8 * 12 * 1024 * 4
+    # dO planes, delta, and 256 bytes for the backward kernel's item counter
+    assert pkg.backward_scratch_bytes(8, 1024, 12, 64) == 2 * 8 * 1024 * 768 * 2 + 8 * 12 * 1024 * 4 + 256
     for bad in [(0, 1, 1, 1), (1, -1, 1, 1), (1, 1, 0, 1), (1, 1, 1, 0), (4096, 4096, 64, 64)]:
         assert pkg.saved_bytes(*bad) == 0
         assert pkg.backward_scratch_bytes(*bad) == 0
