@@ -8,13 +8,21 @@
 // The kernel is persistent: one CTA per SM takes work items from a list.  A work item is one (batch,
 // head) and one tile of 128 keys (K_j, V_j stay in shared memory) together with the query tiles
 // i = j .. last.  Items are ordered heaviest first (key tile 0 sees every query tile); a CTA starts
-// with the item of its own number and takes every further one from a counter in global memory, one
-// item ahead of the one it works on, so an SM that runs slower than the others (the time of the same
-// work differs by +-7 % between SMs) simply takes fewer of the small items at the end.  A fixed deal
-// of the items left the slowest CTA 9 % behind the average.  Barriers, tensor memory and the Q/dO
-// ring live for the whole launch; the K/V tiles of the next item are requested as soon as the last
-// tensor-core instruction that reads the current ones has completed, so that set-up of item w+1
-// overlaps the drain of item w.
+// with the item of its own number, then its mirror image in the second round, and takes every
+// further one from a counter in global memory, two to three items ahead of the one it works on, so
+// an SM that runs slower than the others (the time of the same work differs by +-7 % between SMs)
+// simply takes fewer of the small items at the end.  A fixed deal of the items left the slowest
+// CTA 9 % behind the average.  Barriers, tensor memory and the Q/dO ring live for the whole launch;
+// the K/V tiles of the next item are requested as soon as the last tensor-core instruction that
+// reads the current ones has completed, so that set-up of item w+1 overlaps the drain of item w.
+//
+// The kernel is sensitive to the size of its code: five roles run their loops side by side on one
+// SM, and with the time-out logic of every barrier wait inlined (88 KB of code instead of 74) every
+// query tile took 7 % longer.  That logic is therefore one shared function (tc05.cuh), the items'
+// numbers reach the roles through plain loads behind waits they perform anyway (ItemFeed), and the
+// loops that issue the tensor-core instructions stay fully unrolled all the same: rolling up the
+// three terms of a product, 6 KB less code, cost 22 % (the issuing thread then computes descriptors
+// at run time).
 //
 // Everything is computed transposed so that the key index is the tensor-memory lane:
 //     S^T  = K_j Q_i^T            dP^T = V_j dO_i^T                 (B = Q / dO half, K-major)
@@ -489,10 +497,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             sm.q_raw[0] = (int)blockIdx.x;
             sm.q_raw[1] = p_last;
-            if (nitems > 0) {
-                sm.q_item[0] = (int)blockIdx.x | (p_last < nitems ? kMoreBit : 0);
-                mbar_arrive(&sm.q_full[0]);
-            }
+            sm.q_item[0] = (int)blockIdx.x | (p_last < nitems ? kMoreBit : 0);
+            mbar_arrive(&sm.q_full[0]);
         }
         __syncwarp();
         {
