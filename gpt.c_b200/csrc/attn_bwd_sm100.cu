@@ -800,6 +800,7 @@ cudaError_t launch_fast_backward(const CUtensorMap &map_x, const CUtensorMap &ma
                                  int *sched, int *status, cudaStream_t s) {
     const int nt = (T + kTile - 1) / kTile;
     const long long items = (long long)nt * B * H;
+    if (items >= (long long)kMoreBit) return cudaErrorInvalidValue;  // an item number and a flag share one int
     const unsigned grid = (unsigned)(items < num_sms ? items : num_sms);
     const float scale = 0.125f;  // 1/sqrt(64)
     return launch_after_previous(attn_bwd_kernel, dim3(grid), dim3(kThreads), bwd_smem_bytes(), s, map_x, map_do, map_dx, lse,
