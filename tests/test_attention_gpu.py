@@ -84,6 +84,8 @@ def test_generic_vs_oracle(pkg, gpu, oracle, shape):
 FAST_SHAPES = [
     (1, 128, 1), (1, 1, 1), (2, 2, 2), (1, 127, 1), (1, 129, 2), (2, 130, 2), (1, 256, 1), (2, 200, 3),
     (1, 384, 2), (1, 1024, 2), (3, 640, 1), (8, 128, 12),
+    # more work items than SMs: the backward kernel's thread blocks take several items each from its counter
+    (5, 640, 7), (3, 900, 9),
 ]
 
 
