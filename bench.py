@@ -77,7 +77,7 @@ ROTATE = 4  # buffer sets cycled through so that a set is evicted from L2 before
 REPEATS = 10  # the K-step timed loop is run this many times; median and range are reported
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward core kernel on the bench
 # workload as captured with ncu (profiles/): shown for reference, never as this run's measurement
-BWD_CORE_DRAM_BYTES_PROFILED = {"bytes": 191820288, "source": "profiles/ncu_full_attention_B8_T1024_H12.txt"}
+BWD_CORE_DRAM_BYTES_PROFILED = {"bytes": 193467136, "source": "profiles/ncu_full_attention_B8_T1024_H12.txt"}
 REF_GPTC = os.path.join(ROOT, "oracle", "_ref", "gptc_reference")
 OUR_GPTC = os.path.join(ROOT, "gpt.c_b200", "overlay", "_build", "gptc_overlay")
 
