@@ -351,3 +351,29 @@ def test_backward_item_counter_is_left_at_zero_and_core_only_calls_repeat(pkg, g
     assert counter.tolist() == [0, 0]
     assert torch.equal(dx[:, :, C:], ref[:, :, C:])
     assert pkg.device_status() == 0
+
+
+def _items(B, T, H):
+    return B * H * ((T + 127) // 128)
+
+
+# Shapes whose number of backward work items sits just below, at and just above one, two and three times the
+# number of SMs of a B200 (148), with one to three query tiles per item: the hand-out of the first two fixed
+# items, of the first ones from the counter and of the last ones before the list runs out.
+QUEUE_EDGE_SHAPES = [
+    (7, 128, 21), (4, 128, 37), (149, 100, 1), (5, 128, 59), (8, 128, 37), (297, 64, 1),     # one tile per item
+    (2, 256, 37), (3, 250, 25), (37, 200, 2), (2, 256, 74), (149, 129, 1),                   # two key tiles
+    (7, 384, 7), (1, 300, 50), (5, 384, 10), (2, 384, 74), (3, 257, 50),                     # three key tiles
+]
+
+
+@pytest.mark.parametrize("shape", QUEUE_EDGE_SHAPES, ids=lambda s: "B%d_T%d_H%d_items%d" % (s + (_items(*s),)))
+def test_backward_item_queue_edges_match_generic_kernels(pkg, gpu, shape):
+    """The tensor-core backward against the SIMT kernels of the same library (themselves checked against the
+    oracle above) where the number of work items crosses multiples of the SM count."""
+    B, T, H = shape
+    x, g = seeded(50 + B + T + H, B, T, H, 64)
+    _, _, d1 = run_cuda(pkg, gpu, x, g, H)
+    _, _, d2 = run_cuda(pkg, gpu, x, g, H, flags=pkg.FLAG_FORCE_GENERIC)
+    assert np.isfinite(d1).all()
+    assert np.abs(d1 - d2).max() < EXPECT_DX
